@@ -205,8 +205,15 @@ int citlali_delta_output(const float* o, const float* gate, int gate_stride, con
 int citlali_layer_norm_add(const float* y, const void* gain, int gain_dtype, float* x, void* emit, int emit_dtype, int rows,
                            int hidden, float eps, cudaStream_t stream);
 // out[i] = layer_norm(x[index[i]]) * gain (index may be null: identity).
-int citlali_layer_norm_rows(const float* x, const void* gain, int gain_dtype, const int32_t* row_index, void* out,
-                            int out_dtype, int rows, int hidden, float eps, cudaStream_t stream);
+// bias (of the gain's dtype; may be null) is added.
+int citlali_layer_norm_rows(const float* x, const void* gain, const void* bias, int gain_dtype, const int32_t* row_index,
+                            void* out, int out_dtype, int rows, int hidden, float eps, cudaStream_t stream);
+// x[r] += layer_norm(y[r] + in_bias) * g1 + b1; emit (may be null) receives the updated rows in out_dtype; with g2 also
+// out2[r] = layer_norm(x[r]) * g2 + b2 in out_dtype: the norm behind a sub-layer, the sum, and the norm in front of the next
+// sub-layer in one pass.  in_bias, b1 and b2 may be null; gains and biases are float32.
+int citlali_layer_norm_chain(const float* y, const float* in_bias, const float* g1, const float* b1, float* x, void* emit,
+                             const float* g2, const float* b2, void* out2, int out_dtype, int rows, int hidden, float eps1,
+                             float eps2, cudaStream_t stream);
 // out = x converted from float32.
 int citlali_cast_rows(const float* x, void* out, int out_dtype, size_t n, cudaStream_t stream);
 // out = a l + b r over n floats.
@@ -270,8 +277,21 @@ int citlali_attention_window(const void* q, int q_dtype, const void* k_pool, con
 // weights [rows, E] = softmax(logits) at the `top` best experts among those of the `keep` best of `groups` equal groups of
 // neighbours (a group's score is its largest score; groups <= 1: no groups), 0 elsewhere; chosen [rows, top] (may be
 // null) their indices, best first.
+// The chosen experts' weights are multiplied by weight_scale.
 int citlali_moe_route(const float* logits, float* weights, int32_t* chosen, int rows, int E, int groups, int keep, int top,
-                      cudaStream_t stream);
+                      float weight_scale, cudaStream_t stream);
+// act [rows, E ff + tail_ff] from gate_up [rows, 2 (E ff + tail_ff)], whose columns are, expert after expert, gate and up
+// alternating in runs of `run` (the last expert, which every row uses with weight 1, in runs of `tail_run`).  kind 0:
+// silu(g) u; kind 1: min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, -limit, limit) + 1).  Routed expert e's
+// activations are multiplied by weights[r, e]; where that is zero they are zeros and the inputs are not read.
+int citlali_expert_gate(const void* gate_up, int in_dtype, const float* weights, void* act, int act_dtype, int rows, int E,
+                        int ff, int run, int kind, float limit, float alpha, int tail_ff, int tail_run, float tail_limit,
+                        cudaStream_t stream);
+// out = xielu(z + bias) over [rows, n]: u > 0: ap u^2 + u / 2; u <= 0: an (exp(u) - 1 - u) + u / 2.  bias may be null.
+int citlali_bias_xielu(const void* z, int z_dtype, const float* bias, float ap, float an, void* out, int out_dtype, int rows,
+                       int n, cudaStream_t stream);
+// y[r] += bias over float32 [rows, n].
+int citlali_add_row_bias(float* y, const float* bias, int rows, int n, cudaStream_t stream);
 // act[r, e, :] *= weights[r, e] over act [rows, E, ff].
 int citlali_moe_scale(void* act, int dtype, const float* weights, int rows, int E, int ff, cudaStream_t stream);
 
@@ -303,6 +323,28 @@ int citlali_latent_attention_mma(const float* q, const void* pool, const int32_t
                                  const int32_t* row_slot, const int32_t* row_pos, const float* sink, float* out, int rows,
                                  int H, int R, int E, int page_size, int window, float scale, int splits, float* partial,
                                  size_t partial_floats, cudaStream_t stream);
+
+
+// ---- attention with sigmoid weights on scores that the heads share ---------------------------------------------------
+// proj [rows, C] float32 = q (H D) | k (G D) | v (G V) | gate (H) (k and v only with has_kv, the gate only with has_gate),
+// plus bias [C] (may be null).  q times the row's temperature 1 + temp_coef ln(floor((pos + 1) / temp_every) + 1)
+// (temp_every 0: none) goes to q_out [rows, H D]; k and v go to the paged pools [page, G, page_size, D] / [.., V];
+// gate_out [rows, H] receives the gate's sigmoid.
+int citlali_biased_heads_prepare(const float* proj, const float* bias, const int32_t* row_slot, const int32_t* row_pos,
+                                 const int32_t* page_table, int table_stride, void* k_pool, void* v_pool, int cache_dtype,
+                                 int page_size, void* q_out, int q_dtype, float* gate_out, int rows, int H, int G, int D, int V,
+                                 int has_kv, int has_gate, float temp_coef, int temp_every, cudaStream_t stream);
+// out[r, h, :] = gate[r, h] sum_j sigmoid(sum_g talk[h, g] s_g(j) + head_bias[h]) v_j over the keys j of the row's slot
+// with 0 <= pos - j < window (window 0: all), s_g(j) = (q_g . k_j) scale - 2^(-slope_exp (g + 1) / H) (pos - j).  talk
+// [H, H] (null: identity), head_bias [H] (null: zeros), gate [rows, H] (null: ones) are float32; slope_exp 0: no distance
+// bias.  runs 1: a block a row; more: a block a (row, run of citlali_sigmoid_attention_run_keys() keys) into partial
+// [rows, runs, H V] and a kernel that adds the runs; both give the same bits.
+int citlali_sigmoid_attention_run_keys(void);
+int citlali_sigmoid_attention(const void* q, int q_dtype, const void* k_pool, const void* v_pool, int cache_dtype,
+                              const int32_t* page_table, int table_stride, const int32_t* row_slot, const int32_t* row_pos,
+                              const float* talk, const float* head_bias, const float* gate, void* out, float* partial, int runs,
+                              int rows, int H, int G, int D, int V, int page_size, int window, float scale, float slope_exp,
+                              cudaStream_t stream);
 
 #ifdef __cplusplus
 }

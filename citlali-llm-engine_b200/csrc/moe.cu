@@ -17,7 +17,7 @@ constexpr int kMaxExpertsPerLane = 16;      // E <= 512
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, float* __restrict__ weights, int32_t* __restrict__ chosen, int rows, int E,
-                 int groups, int keep, int top) {
+                 int groups, int keep, int top, float weight_scale) {
     dependents_may_launch();
     wait_for_predecessor();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -118,7 +118,7 @@ moe_route_kernel(const float* __restrict__ logits, float* __restrict__ weights, 
 #pragma unroll
     for (int j = 0; j < kMaxExpertsPerLane; ++j) {
         const int e = lane + 32 * j;
-        if (e < E) weights[(size_t)row * E + e] = (taken >> j & 1u) ? s[j] : 0.0f;
+        if (e < E) weights[(size_t)row * E + e] = (taken >> j & 1u) ? s[j] * weight_scale : 0.0f;
     }
 }
 
@@ -163,7 +163,7 @@ __global__ void moe_scale_vec_kernel(__nv_bfloat16* __restrict__ act, const floa
 using namespace citlali;
 
 extern "C" int citlali_moe_route(const float* logits, float* weights, int32_t* chosen, int rows, int E, int groups, int keep,
-                                 int top, cudaStream_t stream) {
+                                 int top, float weight_scale, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (E <= 0 || E > 32 * kMaxExpertsPerLane || top <= 0 || top > E) {
         set_last_error("moe_route: %d experts (at most %d), %d chosen", E, 32 * kMaxExpertsPerLane, top);
@@ -173,7 +173,7 @@ extern "C" int citlali_moe_route(const float* logits, float* weights, int32_t* c
         set_last_error("moe_route: %d experts in %d groups of which %d are kept cannot give %d experts", E, groups, keep, top);
         return kBadShape;
     }
-    launch_kernel(moe_route_kernel, (rows + 3) / 4, 128, 0, stream, logits, weights, chosen, rows, E, groups, keep, top);
+    launch_kernel(moe_route_kernel, (rows + 3) / 4, 128, 0, stream, logits, weights, chosen, rows, E, groups, keep, top, weight_scale);
     return CITLALI_LAUNCH_CHECK();
 }
 

@@ -46,8 +46,8 @@ layer_norm_add_kernel(const float* __restrict__ y, const TG* __restrict__ gain, 
 
 template <typename TG, typename TO>
 __global__ void __launch_bounds__(256)
-layer_norm_rows_kernel(const float* __restrict__ x, const TG* __restrict__ gain, const int32_t* __restrict__ row_index,
-                       TO* __restrict__ out, int hidden, float eps) {
+layer_norm_rows_kernel(const float* __restrict__ x, const TG* __restrict__ gain, const TG* __restrict__ bias,
+                       const int32_t* __restrict__ row_index, TO* __restrict__ out, int hidden, float eps) {
     extern __shared__ float row_s[];
     __shared__ float scratch[32];
     dependents_may_launch();
@@ -68,7 +68,7 @@ layer_norm_rows_kernel(const float* __restrict__ x, const TG* __restrict__ gain,
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-        stf(out, (size_t)row * hidden + i, (row_s[i] - mean) * inv * ldf(gain, i));
+        stf(out, (size_t)row * hidden + i, (row_s[i] - mean) * inv * ldf(gain, i) + (bias ? ldf(bias, i) : 0.0f));
 }
 
 // The same two kernels for rows that are multiples of 4 and at most 8192 elements: a thread keeps its part of the row in
@@ -99,8 +99,8 @@ __device__ __forceinline__ float4 load4(const TG* p, size_t at) {
 // ADD: x += norm(y) and emit; otherwise out = norm(x[index]).
 template <typename TG, typename TO, bool ADD>
 __global__ void __launch_bounds__(1024)
-layer_norm_vec_kernel(const float* __restrict__ src_rows, const TG* __restrict__ gain, const int32_t* __restrict__ row_index,
-                      float* __restrict__ x, TO* __restrict__ out, int hidden, float eps) {
+layer_norm_vec_kernel(const float* __restrict__ src_rows, const TG* __restrict__ gain, const TG* __restrict__ bias,
+                      const int32_t* __restrict__ row_index, float* __restrict__ x, TO* __restrict__ out, int hidden, float eps) {
     __shared__ float scratch[32];
     dependents_may_launch();
     wait_for_predecessor();
@@ -133,6 +133,10 @@ layer_norm_vec_kernel(const float* __restrict__ src_rows, const TG* __restrict__
         if (qd < quads) {
             const float4 g = load4(gain, (size_t)qd * 4);
             float4 r = make_float4(v[j].x * inv * g.x, v[j].y * inv * g.y, v[j].z * inv * g.z, v[j].w * inv * g.w);
+            if (bias) {
+                const float4 b = load4(bias, (size_t)qd * 4);
+                r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
+            }
             const size_t at = (size_t)row * hidden + qd * 4;
             if (ADD) {
                 const float4 old = *reinterpret_cast<const float4*>(x + at);
@@ -172,6 +176,55 @@ __global__ void scaled_sum_kernel(float a, const float* __restrict__ l, float b,
         out[i] = a * l[i] + b * r[i];
 }
 
+// A norm on a sub-layer's output, the sum, and the norm in front of the next sub-layer in one pass over the row:
+//   x[r] += layer_norm(y[r] + in_bias) * g1 + b1;   emit[r] = x[r] (rounded);   out2[r] = layer_norm(x[r]) * g2 + b2.
+// in_bias, b1, emit and the second norm (g2 null: none; b2 may be null) are optional; gains and biases are float32.  One
+// block a row whose thread count follows the row's length alone; the row waits in shared memory between the passes.
+template <typename TE>
+__global__ void __launch_bounds__(1024)
+layer_norm_chain_kernel(const float* __restrict__ y, const float* __restrict__ in_bias, const float* __restrict__ g1,
+                        const float* __restrict__ b1, float* __restrict__ x, TE* __restrict__ emit, const float* __restrict__ g2,
+                        const float* __restrict__ b2, TE* __restrict__ out2, int hidden, float eps1, float eps2) {
+    extern __shared__ float row_s[];
+    __shared__ float scratch[32];
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x;
+    const float* src = y + (size_t)row * hidden;
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = src[i] + (in_bias ? in_bias[i] : 0.0f);
+        row_s[i] = v;
+        s += v;
+    }
+    const float mean = block_sum(s, scratch) / (float)hidden;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float d = row_s[i] - mean;
+        ss = fmaf(d, d, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps1);
+    float* dst = x + (size_t)row * hidden;
+    float s2 = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = dst[i] + ((row_s[i] - mean) * inv * g1[i] + (b1 ? b1[i] : 0.0f));
+        dst[i] = v;
+        if (emit) stf(emit, (size_t)row * hidden + i, v);
+        row_s[i] = v;
+        s2 += v;
+    }
+    if (g2 == nullptr) return;
+    const float mean2 = block_sum(s2, scratch) / (float)hidden;
+    float ss2 = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float d = row_s[i] - mean2;
+        ss2 = fmaf(d, d, ss2);
+    }
+    const float inv2 = 1.0f / sqrtf(block_sum(ss2, scratch) / (float)hidden + eps2);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        stf(out2, (size_t)row * hidden + i, (row_s[i] - mean2) * inv2 * g2[i] + (b2 ? b2[i] : 0.0f));
+}
+
 static int grid_for(size_t n) {
     const size_t blocks = (n + 255) / 256;
     return (int)(blocks < 8192 ? (blocks ? blocks : 1) : 8192);
@@ -193,7 +246,7 @@ extern "C" int citlali_layer_norm_add(const float* y, const void* gain, int gain
         return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
             return CITLALI_DISPATCH_FLOAT(emit_dtype, TE, [&] {
                 launch_kernel(layer_norm_vec_kernel<TG, TE, true>, rows, vec_threads(rows, hidden), 0, stream, y, (const TG*)gain,
-                              (const int32_t*)nullptr, x, (TE*)emit, hidden, eps);
+                              (const TG*)nullptr, (const int32_t*)nullptr, x, (TE*)emit, hidden, eps);
                 return CITLALI_LAUNCH_CHECK();
             });
         });
@@ -211,19 +264,19 @@ extern "C" int citlali_layer_norm_add(const float* y, const void* gain, int gain
     });
 }
 
-extern "C" int citlali_layer_norm_rows(const float* x, const void* gain, int gain_dtype, const int32_t* row_index, void* out,
-                                       int out_dtype, int rows, int hidden, float eps, cudaStream_t stream) {
+extern "C" int citlali_layer_norm_rows(const float* x, const void* gain, const void* bias, int gain_dtype, const int32_t* row_index,
+                                       void* out, int out_dtype, int rows, int hidden, float eps, cudaStream_t stream) {
     if (rows <= 0) return 0;
     const size_t smem = (size_t)hidden * sizeof(float);
     if (hidden <= 0 || smem > 200 * 1024) {
         set_last_error("layer_norm_rows: rows of %d elements do not fit a block's shared memory", hidden);
         return kTooLarge;
     }
-    if (vec_ok(hidden, x, gain, out, nullptr)) {
+    if (vec_ok(hidden, x, gain, out, bias)) {
         return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
             return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
                 launch_kernel(layer_norm_vec_kernel<TG, TO, false>, rows, vec_threads(rows, hidden), 0, stream, x, (const TG*)gain,
-                              row_index, (float*)nullptr, (TO*)out, hidden, eps);
+                              (const TG*)bias, row_index, (float*)nullptr, (TO*)out, hidden, eps);
                 return CITLALI_LAUNCH_CHECK();
             });
         });
@@ -235,7 +288,7 @@ extern "C" int citlali_layer_norm_rows(const float* x, const void* gain, int gai
                 cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 if (e != cudaSuccess) return (int)e;
             }
-            launch_kernel(kernel, rows, 256, smem, stream, x, (const TG*)gain, row_index, (TO*)out, hidden, eps);
+            launch_kernel(kernel, rows, 256, smem, stream, x, (const TG*)gain, (const TG*)bias, row_index, (TO*)out, hidden, eps);
             return CITLALI_LAUNCH_CHECK();
         });
     });
@@ -253,4 +306,26 @@ extern "C" int citlali_scaled_sum(float a, const float* l, float b, const float*
     if (n == 0) return 0;
     launch_kernel(scaled_sum_kernel, grid_for(n), 256, 0, stream, a, l, b, r, out, n);
     return CITLALI_LAUNCH_CHECK();
+}
+
+extern "C" int citlali_layer_norm_chain(const float* y, const float* in_bias, const float* g1, const float* b1, float* x,
+                                        void* emit, const float* g2, const float* b2, void* out2, int out_dtype, int rows,
+                                        int hidden, float eps1, float eps2, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (hidden <= 0 || smem > 200 * 1024 || g1 == nullptr || (g2 != nullptr && out2 == nullptr)) {
+        set_last_error("layer_norm_chain: rows of %d elements; the first gain and, with a second norm, its output are needed", hidden);
+        return kBadShape;
+    }
+    int threads = ((hidden / 4 + 31) / 32) * 32;             // follows the row's length alone: one order of sums a row
+    threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+    return CITLALI_DISPATCH_FLOAT(out_dtype, TE, [&] {
+        auto kernel = layer_norm_chain_kernel<TE>;
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        launch_kernel(kernel, rows, threads, smem, stream, y, in_bias, g1, b1, x, (TE*)emit, g2, b2, (TE*)out2, hidden, eps1, eps2);
+        return CITLALI_LAUNCH_CHECK();
+    });
 }

@@ -120,19 +120,24 @@ class DecoderModel:
             ops.embed_rows_streams(self.embedding, batch.tokens, x, ctx.error_flag, emb_scale)
         batch.norm_carry = None
         batch.rows_carry = None
+        batch.normed_carry = None
         batch.stream_write = None
+        first_norms = [getattr(block, "first_norm", lambda: None)() for block in self.layers]
         for i, step in enumerate(spec.schedule):
             source = i if step.cache_of is None else step.cache_of
             view = cache.view(source) if cache.has_view(source) else None
             # what the layer before left for this layer's first norm, if it left anything (parts/block.py)
             batch.norm_carry_in, batch.norm_carry = batch.norm_carry, None
             batch.rows_carry_in, batch.rows_carry = batch.rows_carry, None
+            batch.normed_carry_in, batch.normed_carry = batch.normed_carry, None
+            batch.next_first_norm = first_norms[spec.schedule[i + 1].layer] if i + 1 < len(spec.schedule) else None
             if batch.stream_write is not None and not getattr(self.layers[step.layer], "takes_stream_write", False):
                 ops.hyper_write(x, *batch.stream_write)      # the block ahead left a write-back that this one would not do
                 batch.stream_write = None
             self.layers[step.layer].forward(x, batch, view, write_cache=step.cache_of is None)
         batch.norm_carry_in = batch.norm_carry = None
         batch.rows_carry_in = batch.rows_carry = None
+        batch.normed_carry_in = batch.normed_carry = batch.next_first_norm = None
         if batch.stream_write is not None:              # the last layer's last write-back into the streams
             ops.hyper_write(x, *batch.stream_write)
             batch.stream_write = None

@@ -583,15 +583,35 @@ def layer_norm_add(y, gain, eps, x, emit=None):
                                         _stream()), "layer_norm_add")
 
 
-def layer_norm_rows(x, gain, eps, out, row_index=None):
-    _need_cuda(x, gain, out, row_index)
+def layer_norm_rows(x, gain, eps, out, row_index=None, bias=None):
+    """``out = layer_norm(x[row_index]) * gain + bias`` (``bias``, of the gain's dtype, may be None)."""
+    _need_cuda(x, gain, out, row_index, bias)
     rows, hidden = out.shape
     require(x.dtype == torch.float32 and x.shape[1] == hidden and gain.numel() == hidden
             and (row_index is not None or x.shape[0] == rows)
-            and (row_index is None or (row_index.dtype == torch.int32 and row_index.numel() == rows)),
+            and (row_index is None or (row_index.dtype == torch.int32 and row_index.numel() == rows))
+            and (bias is None or (bias.numel() == hidden and bias.dtype == gain.dtype)),
             "layer_norm_rows: shapes or dtypes do not fit")
-    _check(lib().citlali_layer_norm_rows(_ptr(x), _ptr(gain), _i(_dtype_code(gain)), _ptr(row_index), _ptr(out),
+    _check(lib().citlali_layer_norm_rows(_ptr(x), _ptr(gain), _ptr(bias), _i(_dtype_code(gain)), _ptr(row_index), _ptr(out),
                                          _i(_dtype_code(out)), _i(rows), _i(hidden), _f(eps), _stream()), "layer_norm_rows")
+
+
+def layer_norm_chain(y, x, gain, bias, eps, in_bias=None, emit=None, next_gain=None, next_bias=None, next_eps=0.0,
+                     next_out=None):
+    """``x += layer_norm(y + in_bias) * gain + bias``; ``emit`` receives the updated rows; with ``next_gain`` also
+    ``next_out = layer_norm(x) * next_gain + next_bias``.  y, x and all gains and biases are float32; ``emit`` and
+    ``next_out`` share a dtype."""
+    _need_cuda(y, x, gain, bias, in_bias, emit, next_gain, next_bias, next_out)
+    rows, hidden = x.shape
+    vectors = [v for v in (gain, bias, in_bias, next_gain, next_bias) if v is not None]
+    outs = [o for o in (emit, next_out) if o is not None]
+    require(y.dtype == torch.float32 and x.dtype == torch.float32 and y.shape == x.shape
+            and all(v.dtype == torch.float32 and v.numel() == hidden for v in vectors)
+            and all(o.shape == x.shape and o.dtype == outs[0].dtype for o in outs)
+            and (next_gain is None) == (next_out is None), "layer_norm_chain: shapes or dtypes do not fit")
+    _check(lib().citlali_layer_norm_chain(_ptr(y), _ptr(in_bias), _ptr(gain), _ptr(bias), _ptr(x), _ptr(emit), _ptr(next_gain),
+                                          _ptr(next_bias), _ptr(next_out), _i(_dtype_code(outs[0]) if outs else _F32),
+                                          _i(rows), _i(hidden), _f(eps), _f(next_eps), _stream()), "layer_norm_chain")
 
 
 def cast_rows(x, out):
@@ -733,14 +753,14 @@ def attention_window(q, kv, batch, out, nq, nkv, d, vd, window, keep_first, scal
 
 # ---- routed experts -----------------------------------------------------------------------------------------------
 
-def moe_route(logits, weights, groups, keep, top, chosen=None):
+def moe_route(logits, weights, groups, keep, top, chosen=None, weight_scale=1.0):
     _need_cuda(logits, weights, chosen)
     rows, E = logits.shape
     require(logits.dtype == torch.float32 and weights.dtype == torch.float32 and weights.shape == logits.shape
             and (chosen is None or (chosen.dtype == torch.int32 and chosen.shape == (rows, top))),
             "moe_route: shapes or dtypes do not fit")
     _check(lib().citlali_moe_route(_ptr(logits), _ptr(weights), _ptr(chosen), _i(rows), _i(E), _i(int(groups or 0)),
-                                   _i(int(keep or 0)), _i(top), _stream()), "moe_route")
+                                   _i(int(keep or 0)), _i(top), _f(weight_scale), _stream()), "moe_route")
 
 
 def moe_scale(act, weights, ff):
@@ -749,6 +769,84 @@ def moe_scale(act, weights, ff):
     require(act.shape == (rows, E * ff) and weights.dtype == torch.float32, "moe_scale: shapes or dtypes do not fit")
     _check(lib().citlali_moe_scale(_ptr(act), _i(_dtype_code(act)), _ptr(weights), _i(rows), _i(E), _i(ff), _stream()),
            "moe_scale")
+
+
+EXPERT_ACTIVATIONS = {"silu": 0, "clamped_swish": 1}
+
+
+def expert_gate(gate_up, weights, act, E, ff, run, kind, limit=0.0, alpha=1.0, tail_ff=0, tail_run=1, tail_limit=0.0):
+    """The gated activation of ``E`` routed experts (times the row's weight for each) and of a last expert that every row
+    uses, from one product ``gate_up`` [rows, 2 (E ff + tail_ff)] into ``act`` [rows, E ff + tail_ff]."""
+    _need_cuda(gate_up, weights, act)
+    rows = act.shape[0]
+    n = E * ff + tail_ff
+    require(kind in EXPERT_ACTIVATIONS and act.shape == (rows, n) and gate_up.shape == (rows, 2 * n)
+            and (E == 0 or (weights is not None and weights.dtype == torch.float32 and weights.shape == (rows, E))),
+            "expert_gate: shapes or dtypes do not fit")
+    _check(lib().citlali_expert_gate(_ptr(gate_up), _i(_dtype_code(gate_up)), _ptr(weights), _ptr(act), _i(_dtype_code(act)),
+                                     _i(rows), _i(E), _i(ff), _i(run), _i(EXPERT_ACTIVATIONS[kind]), _f(limit), _f(alpha),
+                                     _i(tail_ff), _i(tail_run), _f(tail_limit), _stream()), "expert_gate")
+
+
+def bias_xielu(z, bias, ap, an, out):
+    """``out = xielu(z + bias)``: u > 0: ap u^2 + u / 2; else an (exp(u) - 1 - u) + u / 2.  ``bias`` float32 or None."""
+    _need_cuda(z, bias, out)
+    rows, n = z.shape
+    require(out.shape == z.shape and (bias is None or (bias.dtype == torch.float32 and bias.numel() == n)),
+            "bias_xielu: shapes or dtypes do not fit")
+    _check(lib().citlali_bias_xielu(_ptr(z), _i(_dtype_code(z)), _ptr(bias), _f(ap), _f(an), _ptr(out), _i(_dtype_code(out)),
+                                    _i(rows), _i(n), _stream()), "bias_xielu")
+
+
+def add_row_bias(y, bias):
+    """``y[r] += bias`` over float32 rows."""
+    _need_cuda(y, bias)
+    require(y.dtype == torch.float32 and bias.dtype == torch.float32 and bias.numel() == y.shape[1],
+            "add_row_bias: a float32 matrix and a float32 vector of its row length")
+    _check(lib().citlali_add_row_bias(_ptr(y), _ptr(bias), _i(y.shape[0]), _i(y.shape[1]), _stream()), "add_row_bias")
+
+
+# ---- attention with sigmoid weights --------------------------------------------------------------------------------
+
+def biased_heads_prepare(proj, bias, batch, kv, q_out, gate_out, H, G, D, V, has_kv, temp_coef, temp_every):
+    """Bias, query temperature, cache write and the gate's sigmoid for ``proj`` = q | k | v | gate (float32)."""
+    _need_cuda(proj, bias, kv.keys, kv.values, kv.page_table, q_out, gate_out)
+    rows = proj.shape[0]
+    C = H * D + (G * (D + V) if has_kv else 0) + (H if gate_out is not None else 0)
+    require(proj.dtype == torch.float32 and proj.shape == (rows, C) and q_out.shape == (rows, H * D)
+            and (bias is None or (bias.dtype == torch.float32 and bias.numel() == C))
+            and (gate_out is None or (gate_out.dtype == torch.float32 and gate_out.shape == (rows, H)))
+            and kv.keys.shape[-1] == D and kv.values.shape[-1] == V and kv.keys.shape[-3] == G
+            and kv.keys.dtype == kv.values.dtype, "biased_heads_prepare: shapes or dtypes do not fit")
+    _check(lib().citlali_biased_heads_prepare(
+        _ptr(proj), _ptr(bias), _ptr(batch.row_slot), _ptr(batch.row_pos), _ptr(kv.page_table), _i(kv.page_table.shape[1]),
+        _ptr(kv.keys), _ptr(kv.values), _i(_dtype_code(kv.keys)), _i(kv.page_size), _ptr(q_out), _i(_dtype_code(q_out)),
+        _ptr(gate_out), _i(rows), _i(H), _i(G), _i(D), _i(V), _i(1 if has_kv else 0), _i(1 if gate_out is not None else 0),
+        _f(temp_coef), _i(int(temp_every or 0)), _stream()), "biased_heads_prepare")
+
+
+def sigmoid_attention_run_keys() -> int:
+    return int(lib().citlali_sigmoid_attention_run_keys())
+
+
+def sigmoid_attention(q, kv, batch, talk, head_bias, gate, out, H, G, D, V, window, scale, slope_exp, runs=1):
+    """Every row over its slot's cache with sigmoid weights on scores mixed over the heads.  ``runs`` > 1: the keys of a row
+    are dealt to that many blocks (it must cover the longest row) and a second kernel adds their sums; same bits."""
+    _need_cuda(q, kv.keys, kv.values, kv.page_table, talk, head_bias, gate, out)
+    rows = q.shape[0]
+    require(q.shape == (rows, H * D) and out.shape == (rows, H * V) and q.dtype == out.dtype
+            and (talk is None or (talk.dtype == torch.float32 and talk.shape == (H, H)))
+            and (head_bias is None or (head_bias.dtype == torch.float32 and head_bias.numel() == H))
+            and (gate is None or (gate.dtype == torch.float32 and gate.shape == (rows, H))),
+            "sigmoid_attention: shapes or dtypes do not fit")
+    partial = None
+    if runs > 1:
+        partial = torch.empty((rows, runs, H * V), dtype=torch.float32, device=q.device)
+    _check(lib().citlali_sigmoid_attention(
+        _ptr(q), _i(_dtype_code(q)), _ptr(kv.keys), _ptr(kv.values), _i(_dtype_code(kv.keys)), _ptr(kv.page_table),
+        _i(kv.page_table.shape[1]), _ptr(batch.row_slot), _ptr(batch.row_pos), _ptr(talk), _ptr(head_bias), _ptr(gate),
+        _ptr(out), _ptr(partial), _i(runs), _i(rows), _i(H), _i(G), _i(D), _i(V), _i(kv.page_size), _i(int(window or 0)),
+        _f(scale), _f(slope_exp), _stream()), "sigmoid_attention")
 
 
 # ---- attention through a shared latent -------------------------------------------------------------

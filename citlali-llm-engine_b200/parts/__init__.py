@@ -18,3 +18,7 @@ from .parallel import ParallelMixers
 from .recurrent import GatedRecurrentMixer
 from .ssm import StateSpaceMixer
 from .window_attention import WindowAttention
+from . import sigmoid_attention   # one more built-in mixer
+from .block import SandwichNormBlock
+from .feed_forward import XieluFeedForward
+from .sigmoid_attention import SigmoidAttention

@@ -123,6 +123,12 @@ class StepBatch:
     # (``rows_carry`` -> ``rows_carry_in``, moved by the model like ``norm_carry``).
     rows_carry: Optional[torch.Tensor] = None
     rows_carry_in: Optional[torch.Tensor] = None
+    # The model tells every block which norm the block that runs next begins with (``next_first_norm``, the part itself;
+    # None if that block names none).  A block whose last kernel can run that norm too leaves (normed rows, the norm) as
+    # ``normed_carry``; the next block gets it as ``normed_carry_in`` and uses the rows if the norm is its own first one.
+    normed_carry: Optional[tuple] = None
+    normed_carry_in: Optional[tuple] = None
+    next_first_norm: Optional[object] = None
 
     @property
     def rows(self) -> int:
@@ -153,3 +159,11 @@ def bind_gain(weights, name: str, size: int, ctx: BuildContext) -> torch.Tensor:
     require(tuple(h.shape) == (size,), f"unexpected tensor shape for {name}: got {list(h.shape)}, expected {[size]}")
     dtype = torch.float32 if (ctx.is_float32 or h.dtype == torch.float32) else torch.bfloat16
     return h.tensor.to(device=ctx.device, dtype=dtype).contiguous()
+
+
+def bind_vector(weights, name: str, size: int, ctx: BuildContext) -> torch.Tensor:
+    """A vector that enters 32-bit arithmetic (a bias added to a product's float32 result, a norm's bias, a number per
+    head): float32 on the device in both paths, whatever it is stored in."""
+    h = weights[name]
+    require(tuple(h.shape) == (size,), f"unexpected tensor shape for {name}: got {list(h.shape)}, expected {[size]}")
+    return h.tensor.to(device=ctx.device, dtype=torch.float32).contiguous()

@@ -148,5 +148,82 @@ class SublayerOutputNormBlock:
         return x
 
 
+class SandwichNormBlock:
+    """x += norm_out(mixer(norm_in(x))); x += norm_out'(feed_forward(norm_in'(x))): a norm in front of every sub-layer and
+    another on what it gives.  Parts by name: ``mixer_norm``, ``mixer``, ``mixer_out_norm``, ``feed_forward_norm``,
+    ``feed_forward``, ``feed_forward_out_norm`` (either triple may be absent).  The sub-layers' outputs are float32 and
+    the sum is a 32-bit addition.
+
+    Norms that say ``chain_terms()`` (layer norms; gain, bias, eps) are run in one kernel a sub-layer: the norm on the
+    sub-layer's output, the sum into the residual, and the norm in front of the NEXT sub-layer read and write a row once.
+    The next sub-layer may be the next layer's: this block then leaves the normed rows for it (``StepBatch.normed_carry``:
+    the rows and the norm they went through), and a block that finds rows made by its own first norm skips that norm.  A sub-layer that offers ``deferred_bias`` (its output's bias) has it added in the same kernel.
+    Other norms run one by one (``forward`` in front, ``add_into`` behind)."""
+
+    def __init__(self, layer_spec):
+        has = layer_spec.parts.__contains__
+        self.subs = []
+        for role in ("mixer", "feed_forward"):
+            if has(role):
+                self.subs.append((role, build_part("norm", layer_spec.part(role + "_norm")), build_part(role, layer_spec.part(role)),
+                                  build_part("norm", layer_spec.part(role + "_out_norm"))))
+        self.mixer = next((p for r, _, p, _ in self.subs if r == "mixer"), None)
+
+    def parts(self):
+        return [p for _, before, part, after in self.subs for p in (before, part, after)]
+
+    def tensor_specs(self):
+        return [t for p in self.parts() for t in p.tensor_specs()]
+
+    def cache_requirement(self):
+        return self.mixer.cache_requirement() if self.mixer is not None else None
+
+    def bind(self, weights, ctx):
+        for p in self.parts():
+            p.bind(weights, ctx)
+        self.dtype = ctx.dtype
+        self.chained = all(callable(getattr(n, "chain_terms", None)) for _, before, _, after in self.subs for n in (before, after))
+
+    def first_norm(self):
+        return self.subs[0][1] if self.subs else None
+
+    def forward(self, x, batch, cache_view, write_cache=True):
+        rows, hidden = x.shape
+        h = None
+        carried = batch.normed_carry_in
+        if (self.subs and carried is not None and carried[1] is self.subs[0][1] and carried[0].shape == x.shape
+                and carried[0].dtype == self.dtype):
+            h = carried[0]                    # the block ahead already ran this block's first norm
+        for k, (role, before, part, after) in enumerate(self.subs):
+            if h is None:
+                h = before.forward(x)
+            fresh = bool(getattr(part, "can_overwrite", False))
+            y = (torch.empty if fresh else torch.zeros)((rows, hidden), dtype=torch.float32, device=x.device)
+            extra = {"overwrite": True} if fresh else {}
+            bias = getattr(part, "deferred_bias", None) if self.chained else None
+            if bias is not None:
+                extra["defer_bias"] = True
+            if role == "mixer":
+                part.forward(h, batch, cache_view, y, write_cache, **extra)
+            else:
+                part.forward(h, batch, y, **extra)
+            h = None
+            if not self.chained:
+                after.add_into(y, x)
+                continue
+            nxt = self.subs[k + 1][1] if k + 1 < len(self.subs) else batch.next_first_norm
+            gain, nbias, eps = after.chain_terms()
+            if nxt is not None and callable(getattr(nxt, "chain_terms", None)) and nxt.size == hidden:
+                g2, b2, eps2 = nxt.chain_terms()
+                h = torch.empty((rows, hidden), dtype=self.dtype, device=x.device)
+                ops.layer_norm_chain(y, x, gain, nbias, eps, in_bias=bias, next_gain=g2, next_bias=b2, next_eps=eps2, next_out=h)
+                if k + 1 == len(self.subs):
+                    batch.normed_carry = (h, nxt)
+            else:
+                ops.layer_norm_chain(y, x, gain, nbias, eps, in_bias=bias)
+        return x
+
+
 register_part("block", "pre_norm_residual", PreNormResidualBlock)
+register_part("block", "sandwich_norm", SandwichNormBlock)
 register_part("block", "sublayer_output_norm", SublayerOutputNormBlock)

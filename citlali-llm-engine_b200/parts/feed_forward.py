@@ -8,10 +8,14 @@ Parameters: hidden_size, intermediate_size.
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .. import ops
-from .base import NormedRows, register_part
+from ..errors import require
+from ..weights.loader import TensorSpec
+from .base import NormedRows, bind_vector, register_part
 from .linear import DenseLinear
 
 _RUN = 16
@@ -87,5 +91,67 @@ class SquaredReluFeedForward:
         return residual
 
 
+class XieluFeedForward:
+    """y = W_down xielu(W_up h + b_up) (+ b_down), no gate.  xielu has two numbers p, q stored as one tensor of two:
+    for z > 0: softplus(p) z^2 + z / 2; for z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2.  The up product's result
+    stays float32 until the activation has been applied (bias, activation and the one rounding are one kernel).
+
+    Parameters: hidden_size, intermediate_size; ``names``: {"up", "down", "act", "up_bias", "down_bias"} (a bias name of
+    None: no such bias; defaults ``<prefix>.up``, ``<prefix>.down``, ``<prefix>.act``, ``<prefix>.up.b``,
+    ``<prefix>.down.b``).  A block that adds vectors in a kernel of its own may take the output's bias from
+    ``deferred_bias`` and pass ``defer_bias=True``."""
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, params, prefix: str):
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        n = dict(params.get("names") or {})
+        name = lambda role, default: None if (role in n and n[role] is None) else str(n.get(role) or default)
+        self.act_name = name("act", f"{prefix}.act")
+        self.up_bias_name = name("up_bias", f"{prefix}.up.b")
+        self.down_bias_name = name("down_bias", f"{prefix}.down.b")
+        self.up = DenseLinear([name("up", f"{prefix}.up")], [self.inter], self.hidden)
+        self.down = DenseLinear([name("down", f"{prefix}.down")], [self.hidden], self.inter)
+        self.up_bias = self.deferred_bias = None
+
+    def tensor_specs(self):
+        specs = self.up.tensor_specs() + self.down.tensor_specs() + [TensorSpec(self.act_name, (2,), "state")]
+        if self.up_bias_name is not None:
+            specs.append(TensorSpec(self.up_bias_name, (self.inter,), "state"))
+        if self.down_bias_name is not None:
+            specs.append(TensorSpec(self.down_bias_name, (self.hidden,), "state"))
+        return specs
+
+    def bind(self, weights, ctx):
+        self.up.bind(weights, ctx)
+        self.down.bind(weights, ctx)
+        if self.up_bias_name is not None:
+            self.up_bias = bind_vector(weights, self.up_bias_name, self.inter, ctx)
+        if self.down_bias_name is not None:
+            self.deferred_bias = bind_vector(weights, self.down_bias_name, self.hidden, ctx)
+        h = weights[self.act_name]
+        require(tuple(h.shape) == (2,), f"unexpected tensor shape for {self.act_name}: got {list(h.shape)}, expected [2]")
+        p, q = (float(v) for v in h.tensor.to(torch.float64))
+        softplus = lambda v: v if v > 30.0 else math.log1p(math.exp(v))
+        self.alpha_pos, self.alpha_neg = softplus(p), 0.5 + softplus(q)
+        self.dtype = ctx.dtype
+
+    def forward(self, h, batch, residual, overwrite=False, defer_bias=False):
+        """``overwrite``: ``residual`` holds nothing yet and receives the output.  ``defer_bias``: the caller adds
+        ``deferred_bias`` itself."""
+        z = self.up.forward(h, out_dtype=torch.float32)
+        act = torch.empty((h.shape[0], self.inter), dtype=self.dtype, device=h.device)
+        ops.bias_xielu(z, self.up_bias, self.alpha_pos, self.alpha_neg, act)
+        if overwrite:
+            self.down.forward(act, out=residual)
+        else:
+            self.down.forward(act, accumulate_into=residual)
+        if self.deferred_bias is not None and not defer_bias:
+            ops.add_row_bias(residual, self.deferred_bias)
+        return residual
+
+
 register_part("feed_forward", "gated_silu", GatedSiluFeedForward)
+register_part("feed_forward", "xielu", XieluFeedForward)
 register_part("feed_forward", "relu_squared", SquaredReluFeedForward)

@@ -163,23 +163,38 @@ class BlockDiagonalLinear(DenseLinear):
 class ExpertGateUp(DenseLinear):
     """The gate and up matrices of E experts as one matrix ``[E * 2 * ff, in]``: expert after expert, within an expert
     gate and up rows alternating in runs (of 16 where ff allows, for the product's gate epilogue; else of ff), so that the
-    gated activation comes out as ``[rows, E * ff]``, expert after expert."""
+    gated activation comes out as ``[rows, E * ff]``, expert after expert.  ``tail``: (gate name, up name, width) of one
+    more expert, of a width of its own, whose rows follow the others' (an expert that every row uses)."""
 
-    def __init__(self, gate_names: Sequence[str], up_names: Sequence[str], ff: int, in_features: int):
+    def __init__(self, gate_names: Sequence[str], up_names: Sequence[str], ff: int, in_features: int, tail=None):
         names = [n for pair in zip(gate_names, up_names) for n in pair]
-        super().__init__(names, [ff] * len(names), in_features)
+        splits = [ff] * len(names)
+        self.tail_ff = 0
+        if tail is not None:
+            self.tail_ff = int(tail[2])
+            names += [str(tail[0]), str(tail[1])]
+            splits += [self.tail_ff, self.tail_ff]
+        super().__init__(names, splits, in_features)
         self.experts, self.ff = len(gate_names), int(ff)
         self.run = 16 if ff % 16 == 0 else int(ff)
+        self.tail_run = (16 if self.tail_ff % 16 == 0 else self.tail_ff) if self.tail_ff else 1
 
     def bind(self, weights, ctx):
         E, ff, r = self.experts, self.ff, self.run
         w = torch.empty((self.out_features, self.in_features), dtype=ctx.dtype, device=ctx.device)
-        runs = w.view(E, ff // r, 2, r, self.in_features)       # [expert, run, gate or up, row in run, in]
-        for k, n in enumerate(self.names):
+        routed = w[:E * 2 * ff]
+        runs = routed.view(E, ff // r, 2, r, self.in_features)       # [expert, run, gate or up, row in run, in]
+        tail_runs = None
+        if self.tail_ff:
+            tail_runs = w[E * 2 * ff:].view(self.tail_ff // self.tail_run, 2, self.tail_run, self.in_features)
+        for k, (n, o) in enumerate(zip(self.names, self.out_splits)):
             h = weights[n]
-            require(tuple(h.shape) == (ff, self.in_features),
-                    f"unexpected tensor shape for {n}: got {list(h.shape)}, expected {[ff, self.in_features]}")
-            h.copy_into(runs[k // 2, :, k % 2])
+            require(tuple(h.shape) == (o, self.in_features),
+                    f"unexpected tensor shape for {n}: got {list(h.shape)}, expected {[o, self.in_features]}")
+            if k < 2 * E:
+                h.copy_into(runs[k // 2, :, k % 2])
+            else:
+                h.copy_into(tail_runs[:, k - 2 * E])
         self.weight = w
         self.dtype = ctx.dtype
         self.error_flag = ctx.error_flag
@@ -187,22 +202,31 @@ class ExpertGateUp(DenseLinear):
 
 class ExpertDown(DenseLinear):
     """The output matrices of E experts side by side, ``[out, E * ff]``: applied to activations that were multiplied by
-    each expert's weight, one product gives the weighted sum of the experts' outputs."""
+    each expert's weight, one product gives the weighted sum of the experts' outputs.  ``tail``: (name, width) of one more
+    expert's output matrix, of a width of its own, behind the others'."""
 
-    def __init__(self, names: Sequence[str], ff: int, out_features: int):
-        super().__init__(names, [out_features], len(names) * int(ff))
+    def __init__(self, names: Sequence[str], ff: int, out_features: int, tail=None):
+        self.tail_ff = int(tail[1]) if tail is not None else 0
+        self.routed = len(names)
+        names = list(names) + ([str(tail[0])] if tail is not None else [])
+        super().__init__(names, [out_features], self.routed * int(ff) + self.tail_ff)
         self.ff = int(ff)
 
+    def _widths(self):
+        return [self.ff] * self.routed + ([self.tail_ff] if self.tail_ff else [])
+
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(n, (self.out_features, self.ff), "matrix") for n in self.names]
+        return [TensorSpec(n, (self.out_features, f), "matrix") for n, f in zip(self.names, self._widths())]
 
     def bind(self, weights, ctx):
         w = torch.empty((self.out_features, self.in_features), dtype=ctx.dtype, device=ctx.device)
-        for e, n in enumerate(self.names):
+        at = 0
+        for n, f in zip(self.names, self._widths()):
             h = weights[n]
-            require(tuple(h.shape) == (self.out_features, self.ff),
-                    f"unexpected tensor shape for {n}: got {list(h.shape)}, expected {[self.out_features, self.ff]}")
-            h.copy_into(w[:, e * self.ff:(e + 1) * self.ff])
+            require(tuple(h.shape) == (self.out_features, f),
+                    f"unexpected tensor shape for {n}: got {list(h.shape)}, expected {[self.out_features, f]}")
+            h.copy_into(w[:, at:at + f])
+            at += f
         self.weight = w
         self.dtype = ctx.dtype
         self.error_flag = ctx.error_flag
