@@ -1,7 +1,9 @@
 """Throughput of a decoder design beside another of the library's designs at equal size, with every kernel of a step timed.
 
-Used by ``bench.py --design lanizen`` (beside the Qwen3 dense decoder) and ``--design gidirax`` (beside Lanizen, the
-closest design the library has: both mix delta-rule layers with windowed attention).  A size is a width and a number of layers; both models get that width, that
+Used by ``bench.py --design lanizen`` (beside the Qwen3 dense decoder), ``--design gidirax`` (beside Lanizen, the
+closest design the library has: both mix delta-rule layers with windowed attention) and ``--design sobunex`` (beside
+Gidirax: both have windowed attention with key and value sizes of their own, layer norms on the sub-layers' outputs and
+experts whose weights are not renormalised).  A size is a width and a number of layers; both models get that width, that
 many layers, feed-forwards of equal parameter count (8 width^2: two matrices of 4 width, or three of 8/3 width) and
 the same vocabulary, with random weights in bfloat16.  Measured per model: one prompt in one step (tokens a second),
 one decode step of ``batch`` sequences at ``context`` through the session's ``decode`` (the replayed graph where the
@@ -59,6 +61,23 @@ def gidirax_config(width: int, layers: int, vocab: int, window: int = 1024):
     order = [delta, ssm, par, delta]
     return config_from_dict({"architecture": "Gidirax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
                              "layers": [order[i % 4] for i in range(layers)]})
+
+
+def sobunex_config(width: int, layers: int, vocab: int, window: int = 1024):
+    """Attention layers only, in pairs: one with keys and values of its own and a dense feed-forward of 4 x width, one that
+    reads the first one's keys and has sixteen experts of which a token uses four, plus an expert for every row (about
+    8 width^2 parameters in a layer's experts).  Heads of 128, four query heads a key/value head."""
+    heads = max(1, width // 128)
+    ff = max(64, (width // 6 + 32) // 64 * 64)
+    mixer = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+             "mask": {"size": window}, "q_temp": {"coef": 0.1, "every": 512}}
+    own = {"type": "attention", "mixer": dict(mixer), "mlp": {"kind": "dense", "ff": 4 * width}}
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": 16, "top": 4, "scale": 2.0},
+           "shared": {"ff": 2 * ff, "limit": 7.0}}
+    out = []
+    for i in range(layers):
+        out.append(own if i % 2 == 0 else {"type": "attention", "mixer": dict(mixer, kv_from=i - 1), "mlp": moe})
+    return config_from_dict({"architecture": "Sobunex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": out})
 
 
 def qwen3_config(width: int, layers: int, vocab: int):
@@ -188,7 +207,8 @@ def measure_model(config, prompt_tokens: int, batch: int, context: int, steps: i
     return out
 
 
-DESIGNS = {"lanizen": (lanizen_config, "qwen3"), "gidirax": (gidirax_config, "lanizen"), "qwen3": (qwen3_config, None)}
+DESIGNS = {"lanizen": (lanizen_config, "qwen3"), "gidirax": (gidirax_config, "lanizen"), "sobunex": (sobunex_config, "gidirax"),
+           "qwen3": (qwen3_config, None)}
 
 
 def run(design: str, sizes, prompt_tokens: int, batch: int, context: int, steps: int, warmup: int) -> dict:

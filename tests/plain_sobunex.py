@@ -79,7 +79,7 @@ def sigmoid_weights(s, pb, mask):
 
 
 def attention_keys_values(h, w, p, m):
-    G, D = m["kv_heads"], m["dim"]
+    G, D = m.get("kv_heads") or m["heads"], m["dim"]
     V = m.get("vdim") or D
     T = h.shape[0]
     return linear(h, w, p + ".k").view(T, G, D), linear(h, w, p + ".v").view(T, G, V)
@@ -89,7 +89,7 @@ def attention_mixer(h, w, p, m, kv=None, store=None):
     """``kv``: the (keys, values) of the layer this one borrows from (None: its own).  ``store``: how keys and values are
     rounded when they are kept (None: not at all)."""
     T = h.shape[0]
-    H, G, D = m["heads"], m["kv_heads"], m["dim"]
+    H, G, D = m["heads"], m.get("kv_heads") or m["heads"], m["dim"]
     V = m.get("vdim") or D
     q = linear(h, w, p + ".q").view(T, H, D)
     if kv is None:
