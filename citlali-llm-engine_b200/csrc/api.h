@@ -346,6 +346,19 @@ int citlali_sigmoid_attention(const void* q, int q_dtype, const void* k_pool, co
                               int rows, int H, int G, int D, int V, int page_size, int window, float scale, float slope_exp,
                               cudaStream_t stream);
 
+// The same attention for runs of new tokens of `sequences` sequences (rows as citlali_attention_prefill takes them) on the
+// tensor cores: bfloat16 q, pools and out, pages of 64.  One kernel writes every head's weights to `weights` (scratch of
+// H * groups * columns * 8 bfloat16; columns and groups from the two functions below), a second one multiplies them with the
+// values.  The weights are rounded to bfloat16 for that product; everything before is float32 on bfloat16 q and keys.
+int citlali_sigmoid_attention_mma_supports(int H, int G, int D, int V, int page_size);
+int citlali_sigmoid_attention_mma_columns(int window, int max_keys);
+int citlali_sigmoid_attention_mma_groups(int rows, int sequences);
+int citlali_sigmoid_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int32_t* page_table,
+                                  int table_stride, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_past,
+                                  const float* talk, const float* head_bias, const float* gate, void* out, void* weights,
+                                  int columns, int groups, int sequences, int max_new, int H, int G, int D, int V, int page_size,
+                                  int window, float scale, float slope_exp, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -849,6 +849,41 @@ def sigmoid_attention(q, kv, batch, talk, head_bias, gate, out, H, G, D, V, wind
         _f(scale), _f(slope_exp), _stream()), "sigmoid_attention")
 
 
+def sigmoid_attention_mma_supports(H, G, D, V, page_size) -> bool:
+    return bool(lib().citlali_sigmoid_attention_mma_supports(_i(H), _i(G), _i(D), _i(V), _i(page_size)))
+
+
+def sigmoid_attention_mma_scratch_bytes(rows, sequences, max_keys, H, window) -> int:
+    """Bytes of the weights that ``sigmoid_attention_mma`` keeps between its two kernels."""
+    l = lib()
+    columns = int(l.citlali_sigmoid_attention_mma_columns(_i(int(window or 0)), _i(max_keys)))
+    groups = int(l.citlali_sigmoid_attention_mma_groups(_i(rows), _i(sequences)))
+    return H * groups * columns * 8 * 2
+
+
+def sigmoid_attention_mma(q, kv, batch, talk, head_bias, gate, out, H, G, D, V, window, scale, slope_exp):
+    """``sigmoid_attention`` for runs of new tokens on the tensor cores (bfloat16): every head's weights go to a scratch
+    buffer, a second kernel multiplies them with the values."""
+    _need_cuda(q, kv.keys, kv.values, kv.page_table, talk, head_bias, gate, out)
+    rows = q.shape[0]
+    require(q.dtype == torch.bfloat16 and kv.keys.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+            and q.shape == (rows, H * D) and out.shape == (rows, H * V) and q.is_contiguous() and out.is_contiguous()
+            and (talk is None or (talk.dtype == torch.float32 and talk.shape == (H, H)))
+            and (head_bias is None or (head_bias.dtype == torch.float32 and head_bias.numel() == H))
+            and (gate is None or (gate.dtype == torch.float32 and gate.shape == (rows, H))),
+            "sigmoid_attention_mma: shapes or dtypes do not fit")
+    l = lib()
+    sequences = len(batch.slots)
+    columns = int(l.citlali_sigmoid_attention_mma_columns(_i(int(window or 0)), _i(max(batch.max_keys, 1))))
+    groups = int(l.citlali_sigmoid_attention_mma_groups(_i(rows), _i(sequences)))
+    weights = _scratch(q.device, "sigmoid attention weights", H * groups * columns * 8 * 2)
+    _check(l.citlali_sigmoid_attention_mma(
+        _ptr(q), _ptr(kv.keys), _ptr(kv.values), _ptr(kv.page_table), _i(kv.page_table.shape[1]), _ptr(batch.seq_start),
+        _ptr(batch.seq_slot), _ptr(batch.seq_past), _ptr(talk), _ptr(head_bias), _ptr(gate), _ptr(out), _ptr(weights),
+        _i(columns), _i(groups), _i(sequences), _i(max(batch.n_new)), _i(H), _i(G), _i(D), _i(V), _i(kv.page_size),
+        _i(int(window or 0)), _f(scale), _f(slope_exp), _stream()), "sigmoid_attention_mma")
+
+
 # ---- attention through a shared latent -------------------------------------------------------------
 
 def latent_prepare(proj, RQ, R, P, has_kv, q_weight, c_weight, inv_freq, rot_dims, row_slot, row_pos, page_table, pool,

@@ -18,9 +18,12 @@ A mixer with ``own_kv`` False has no key and value projections: it is given anot
 of those that read its cache; None: everything is kept).
 
 How it runs: one product for q | k | v | gate with a float32 result; one kernel adds the biases, applies the temperature,
-writes k and v to the paged cache and takes the gate's sigmoid; one kernel a row does scores, mix, sigmoid and the sums in
-float32 over the cache (rows of a prompt and single tokens alike, in an order of sums that depends on the row's position and
-the window alone); then the output product.
+writes k and v to the paged cache and takes the gate's sigmoid.  Single tokens, and everything in 32-bit: one kernel a row
+does scores, mix, sigmoid and the sums in float32 over the cache, in an order of sums that depends on the row's position
+and the window alone.  Runs of new tokens in bfloat16 (``mma_min_rows`` rows or more): two tensor-core kernels, one that
+writes all heads' weights of 8 rows and a run of pages (scores by MMA, mix and sigmoid in float32, rounded to bfloat16), one
+that multiplies them with the values a head and 64 rows at a time; the weights in between take at most ``mma_max_scratch``
+bytes, else the first form runs.  Then the output product.
 
 Parameters: hidden_size, heads, kv_heads, dim, vdim, scale, window, cache_window, q_temp, slope_exp, own_kv, talk,
 head_bias, gate, biases; ``names``: full tensor names by role (q, k, v, o, talk, head_bias, gate, q_bias, k_bias, v_bias,
@@ -82,11 +85,23 @@ class SigmoidAttention:
         self.proj = DenseLinear(stacked, sizes, self.hidden)
         self.o = DenseLinear([nm["o"]], [self.hidden], self.H * self.V)
         self.bias = self.deferred_bias = self.talk = self.head_bias = None
+        self.mma_min_rows = int(params.get("mma_min_rows", 64))            # fewer rows a step: the kernel a row
+        self.mma_max_scratch = int(params.get("mma_max_scratch", 2 << 30))   # bytes of weights between the two kernels
 
     @property
     def graph_safe(self):
         # with a window the launch depends on the row count alone; without one the runs follow the longest row
         return self.window is not None
+
+    def _on_tensor_cores(self, batch, kv, rows) -> bool:
+        """Runs of new tokens in bfloat16 go to the two tensor-core kernels when these have the sizes and the weights they
+        keep in between stay small; single tokens, 32-bit and everything else go to the kernel that walks a row's keys."""
+        if self.dtype != torch.bfloat16 or rows < self.mma_min_rows or rows < 8 * len(batch.slots):
+            return False
+        if not ops.sigmoid_attention_mma_supports(self.H, self.G, self.D, self.V, kv.page_size):
+            return False
+        need = ops.sigmoid_attention_mma_scratch_bytes(rows, len(batch.slots), max(batch.max_keys, 1), self.H, self.window)
+        return need <= self.mma_max_scratch
 
     def _bias_names(self):
         nm = self.names
@@ -141,12 +156,16 @@ class SigmoidAttention:
         ops.biased_heads_prepare(proj, self.bias, batch, kv, q, gate, self.H, self.G, self.D, self.V, self.own_kv,
                                  self.temp_coef, self.temp_every)
         out = torch.empty((rows, self.H * self.V), dtype=self.dtype, device=proj.device)
-        # few rows: a row's keys are dealt to several blocks, as many as the window (or, without one, the longest row) has
-        # runs; with a window the launch then depends on the row count alone
-        reach = self.window if self.window is not None else max(batch.max_keys, 1)
-        runs = (reach + self.run_keys - 1) // self.run_keys if rows < 512 else 1
-        ops.sigmoid_attention(q, kv, batch, self.talk, self.head_bias, gate, out, self.H, self.G, self.D, self.V, self.window,
-                              self.scale, self.slope_exp, runs=runs)
+        if self._on_tensor_cores(batch, kv, rows):
+            ops.sigmoid_attention_mma(q, kv, batch, self.talk, self.head_bias, gate, out, self.H, self.G, self.D, self.V,
+                                      self.window, self.scale, self.slope_exp)
+        else:
+            # few rows: a row's keys are dealt to several blocks, as many as the window (or, without one, the longest row)
+            # has runs; with a window the launch then depends on the row count alone
+            reach = self.window if self.window is not None else max(batch.max_keys, 1)
+            runs = (reach + self.run_keys - 1) // self.run_keys if rows < 512 else 1
+            ops.sigmoid_attention(q, kv, batch, self.talk, self.head_bias, gate, out, self.H, self.G, self.D, self.V,
+                                  self.window, self.scale, self.slope_exp, runs=runs)
         if overwrite:
             self.o.forward(out, out=residual)
         else:

@@ -490,3 +490,74 @@ def test_block_with_norms_on_both_sides_of_every_sublayer(with_ff, dtype):
         cache.release(slot)
         close(torch.cat(rows), want, dtype, f"block {dtype} {len(portions)} portions")
     assert not any(ctx.error_flag.tolist())
+
+
+MMA = [
+    # head counts that are no multiple of eight, keys and values of different sizes, a window inside one page
+    dict(hidden_size=48, heads=6, kv_heads=3, dim=48, vdim=80, scale=0.15, window=40, q_temp={"coef": 0.4, "every": 5}),
+    # a window over several pages that ends inside a page, one key/value head
+    dict(hidden_size=64, heads=8, kv_heads=1, dim=32, vdim=16, scale=0.2, window=150, q_temp=None),
+    # no window, the largest head size
+    dict(hidden_size=32, heads=2, kv_heads=2, dim=256, vdim=32, scale=0.06, window=None, q_temp={"coef": 0.2, "every": 64}),
+    # twelve heads, a window of exactly two pages; no mix and no gate
+    dict(hidden_size=96, heads=12, kv_heads=4, dim=16, vdim=128, scale=0.3, window=128, q_temp=None, talk=False, gate=False),
+]
+
+
+@pytest.mark.parametrize("params", MMA)
+def test_tensor_core_form_of_new_tokens(params):
+    """Runs of new tokens in bfloat16 take the two tensor-core kernels; the same rows through the kernel that walks a row's
+    keys, and the plain implementation, must agree: whole prompts, portions that start inside a group of rows and inside a
+    page, unequal sequences in one step (the second starts at a row that is no multiple of eight), a slot used again."""
+    dtype = torch.bfloat16
+    T = 333
+    params = dict(params, slope_exp=8.0)
+    h, other = inputs(T, params["hidden_size"], 21), inputs(77, params["hidden_size"], 22)
+    fast = Harness(dict(params, mma_min_rows=8), dtype, seed=9, capacity=2048)
+    slow = Harness(dict(params, mma_min_rows=10 ** 9), dtype, weights=fast.weights, capacity=2048)
+    taken = []
+    real = ops.sigmoid_attention_mma
+    ops.sigmoid_attention_mma = lambda *a, **k: (taken.append(a[0].shape[0]), real(*a, **k))[1]
+    try:
+        fn = plain_mixer(params, "m")
+        want, want_other = fn(h, fast.weights), fn(other, fast.weights)
+        for portions in ([{"a": T}], [{"a": 13}, {"a": 120}, {"a": 1}, {"a": 9}, {"a": 190}], [{"a": 64}, {"a": 64}, {"a": 205}]):
+            got = fast.run({"a": h}, portions)[0]["a"]
+            ref = slow.run({"a": h}, portions)[0]["a"]
+            close(got, want, dtype, f"tensor cores {portions}")
+            close(got, ref, dtype, f"tensor cores against rows {portions}")
+        assert taken and 1 not in taken and 13 in taken and 333 in taken
+        both = fast.run({"a": h, "b": other}, [{"a": 101, "b": 30}, {"a": 1, "b": 1}, {"a": 231, "b": 46}])[0]
+        close(both["a"], want, dtype, "batched a")
+        close(both["b"], want_other, dtype, "batched b")
+        again = fast.run({"c": other}, [{"c": 77}])[0]["c"]
+        close(again, want_other, dtype, "reused slot")
+        n = len(taken)
+        slow.run({"a": h}, [{"a": T}])
+        assert len(taken) == n
+    finally:
+        ops.sigmoid_attention_mma = real
+
+
+@pytest.mark.parametrize("window", [9, 64, 65, 130, 1, None])
+def test_window_edges_on_the_tensor_cores(window):
+    """The key that stands out, with every portion on the tensor-core kernels: the row at distance window - 1 has it, the next
+    one has lost it, also when the key came in an earlier portion and when the edge falls between two groups of rows."""
+    d, T = 16, 210
+    params, weights = standing_out(d, window)
+    params = dict(params, mma_min_rows=8)
+    for special in (0, 7, 8, 63, 64, 100):
+        g = torch.Generator().manual_seed(special)
+        h = 0.05 * torch.randn(T, d, generator=g)
+        h[:, 0] = 1.0
+        h[special, 0] = 30.0
+        h[special, 1] = 7.0
+        h = h.to(torch.bfloat16).double()
+        want = plain_mixer(params, "m")(h, weights)
+        see = plain.visible(T, window)
+        for portions in ([{"a": T}], [{"a": 101}, {"a": 109}], [{"a": 9}, {"a": 60}, {"a": 141}]):
+            got = Harness(params, torch.bfloat16, weights=weights).run({"a": h}, portions)[0]["a"]
+            allowed = 0.03 * want.abs().amax(-1, keepdim=True).clamp(min=1.0)
+            assert bool(((got - want).abs() <= allowed).all()), (window, special, portions)
+            for i in range(special + 1, T):
+                assert (float(got[i][1]) > 3.0) == bool(see[i, special]), (window, special, i)
