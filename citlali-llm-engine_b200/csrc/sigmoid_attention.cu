@@ -23,8 +23,23 @@
 namespace citlali {
 
 constexpr int kTileKeys = 32;          // keys whose scores wait in shared memory at a time
-constexpr int kRunKeys = 128;          // keys of a run (a multiple of kTileKeys)
+constexpr int kRunKeys = 32;           // keys of a run (a multiple of kTileKeys)
 constexpr int kSigThreads = 256;
+
+// Eight consecutive elements as floats, by 16-byte loads (the address is a multiple of eight elements).
+__device__ __forceinline__ void load8(const float* p, float (&x)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&x)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        x[2 * i] = __uint_as_float(w[i] << 16);
+        x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
 
 template <typename T, typename TQ>
 __global__ void __launch_bounds__(256)
@@ -60,17 +75,20 @@ biased_heads_prepare_kernel(const float* __restrict__ proj, const float* __restr
     }
 }
 
-// PL: elements of a key a lane holds (D <= 32 PL).  ACC: outputs a thread owns (H V <= 256 ACC).
-template <typename T, typename TQ, int PL, int ACC>
+// PL: elements of a key a lane holds (D <= 32 PL).  ACC: outputs a thread owns (H V <= 256 ACC).  VEC (D and V multiples
+// of eight): keys and values come in 16-byte pieces; eight lanes share a key's score (four keys a warp at a time) and a
+// thread owns eight neighbouring outputs of one head.  Either way an output's keys are added in ascending order.
+template <typename T, typename TQ, int PL, int ACC, bool VEC>
 __global__ void __launch_bounds__(kSigThreads)
 sigmoid_attention_kernel(const TQ* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                          const int32_t* __restrict__ page_table, int table_stride, const int32_t* __restrict__ row_slot,
                          const int32_t* __restrict__ row_pos, const float* __restrict__ talk, const float* __restrict__ head_bias,
                          const float* __restrict__ gate, TQ* __restrict__ out, float* __restrict__ partial, int H, int G, int D,
                          int V, int page_size, int window, float scale, float slope_exp) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
+    constexpr int NACC = VEC ? (ACC >= 8 ? ACC : 8) : ACC;
     float* qs = smem;                                  // [H, D]
-    float* tk = qs + H * D;                            // [H, H]
+    float* tk = qs + H * D;                            // [H (g), H (h)]: the mix, transposed
     float* hb = tk + H * H;                            // [H]
     float* sl = hb + H;                                // [H]
     float* raw = sl + H;                               // [kTileKeys, H]
@@ -87,48 +105,90 @@ sigmoid_attention_kernel(const TQ* __restrict__ q, const T* __restrict__ k_pool,
     if (split && (int)blockIdx.y >= runs) return;
     const int HV = H * V, per = H / G;
     for (int i = tid; i < H * D; i += kSigThreads) qs[i] = ldf(q, (size_t)row * H * D + i);
-    for (int i = tid; i < H * H; i += kSigThreads) tk[i] = talk ? talk[i] : ((i / H == i % H) ? 1.0f : 0.0f);
+    for (int i = tid; i < H * H; i += kSigThreads) tk[i] = talk ? talk[(i % H) * H + i / H] : ((i / H == i % H) ? 1.0f : 0.0f);
     for (int i = tid; i < H; i += kSigThreads) {
         hb[i] = head_bias ? head_bias[i] : 0.0f;
         sl[i] = slope_exp > 0.0f ? exp2f(-slope_exp * (float)(i + 1) / (float)H) : 0.0f;
     }
     __syncthreads();
     const int32_t* pages = page_table + (size_t)row_slot[row] * table_stride;
-    float total[ACC];
+    float total[NACC];
 #pragma unroll
-    for (int a = 0; a < ACC; ++a) total[a] = 0.0f;
+    for (int a = 0; a < NACC; ++a) total[a] = 0.0f;
     const int run_first = split ? blockIdx.y : 0, run_last = split ? blockIdx.y + 1 : runs;
     for (int run = run_first; run < run_last; ++run) {
-        float acc[ACC];
+        float acc[NACC];
 #pragma unroll
-        for (int a = 0; a < ACC; ++a) acc[a] = 0.0f;
+        for (int a = 0; a < NACC; ++a) acc[a] = 0.0f;
         const int k0 = lo + run * kRunKeys;
         const int k1 = min(k0 + kRunKeys, pos + 1);
         for (int t0 = k0; t0 < k1; t0 += kTileKeys) {
             const int tn = min(kTileKeys, k1 - t0);
-            // scores of the tile's keys: a warp a key, a lane the elements lane, lane + 32, ... of it
-            for (int jj = warp; jj < tn; jj += kSigThreads / 32) {
+            if constexpr (VEC) {
+                // scores of the tile's keys: eight lanes a key, a lane the elements 8 l, 8 l + 64, ... of it
+                constexpr int PL8 = PL / 2;
+                const int jj = warp * 4 + (lane >> 3), l8 = lane & 7;
+                const bool ok = jj < tn;
                 const int key = t0 + jj;
-                const int base = pages[key / page_size] * G * page_size + key % page_size;
-                if (lane == 0) rowbase[jj] = base;
+                const int base = ok ? pages[key / page_size] * G * page_size + key % page_size : 0;
+                if (ok && l8 == 0) rowbase[jj] = base;
                 for (int g2 = 0; g2 < G; ++g2) {
                     const size_t at = ((size_t)base + (size_t)g2 * page_size) * (size_t)D;
-                    float kr[PL];
+                    float kr[PL8][8];
 #pragma unroll
-                    for (int c = 0; c < PL; ++c) {
-                        const int i = lane + 32 * c;
-                        kr[c] = i < D ? ldf(k_pool, at + i) : 0.0f;
+                    for (int c = 0; c < PL8; ++c) {
+                        const int i = 8 * l8 + 64 * c;
+                        if (ok && i < D) load8(k_pool + at + i, kr[c]);
+                        else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) kr[c][e] = 0.0f;
+                        }
                     }
                     for (int hh = 0; hh < per; ++hh) {
                         const int h = g2 * per + hh;
                         float s = 0.0f;
 #pragma unroll
+                        for (int c = 0; c < PL8; ++c) {
+                            const int i = 8 * l8 + 64 * c;
+                            if (i < D) {
+                                const float4 qa = *reinterpret_cast<const float4*>(qs + h * D + i);
+                                const float4 qb = *reinterpret_cast<const float4*>(qs + h * D + i + 4);
+                                s = fmaf(qa.x, kr[c][0], s); s = fmaf(qa.y, kr[c][1], s); s = fmaf(qa.z, kr[c][2], s);
+                                s = fmaf(qa.w, kr[c][3], s); s = fmaf(qb.x, kr[c][4], s); s = fmaf(qb.y, kr[c][5], s);
+                                s = fmaf(qb.z, kr[c][6], s); s = fmaf(qb.w, kr[c][7], s);
+                            }
+                        }
+                        s += __shfl_xor_sync(0xffffffffu, s, 1);
+                        s += __shfl_xor_sync(0xffffffffu, s, 2);
+                        s += __shfl_xor_sync(0xffffffffu, s, 4);
+                        if (ok && l8 == 0) raw[jj * H + h] = s * scale - sl[h] * (float)(pos - key);
+                    }
+                }
+            } else {
+                // scores of the tile's keys: a warp a key, a lane the elements lane, lane + 32, ... of it
+                for (int jj = warp; jj < tn; jj += kSigThreads / 32) {
+                    const int key = t0 + jj;
+                    const int base = pages[key / page_size] * G * page_size + key % page_size;
+                    if (lane == 0) rowbase[jj] = base;
+                    for (int g2 = 0; g2 < G; ++g2) {
+                        const size_t at = ((size_t)base + (size_t)g2 * page_size) * (size_t)D;
+                        float kr[PL];
+#pragma unroll
                         for (int c = 0; c < PL; ++c) {
                             const int i = lane + 32 * c;
-                            if (i < D) s = fmaf(qs[h * D + i], kr[c], s);
+                            kr[c] = i < D ? ldf(k_pool, at + i) : 0.0f;
                         }
-                        s = warp_sum(s);
-                        if (lane == 0) raw[jj * H + h] = s * scale - sl[h] * (float)(pos - key);
+                        for (int hh = 0; hh < per; ++hh) {
+                            const int h = g2 * per + hh;
+                            float s = 0.0f;
+#pragma unroll
+                            for (int c = 0; c < PL; ++c) {
+                                const int i = lane + 32 * c;
+                                if (i < D) s = fmaf(qs[h * D + i], kr[c], s);
+                            }
+                            s = warp_sum(s);
+                            if (lane == 0) raw[jj * H + h] = s * scale - sl[h] * (float)(pos - key);
+                        }
                     }
                 }
             }
@@ -137,33 +197,54 @@ sigmoid_attention_kernel(const TQ* __restrict__ q, const T* __restrict__ k_pool,
             for (int i = tid; i < tn * H; i += kSigThreads) {
                 const int jj = i / H, h = i % H;
                 float m = 0.0f;
-                for (int g = 0; g < H; ++g) m = fmaf(tk[h * H + g], raw[jj * H + g], m);
+                for (int g = 0; g < H; ++g) m = fmaf(tk[g * H + h], raw[jj * H + g], m);
                 m += hb[h];
                 wts[i] = 1.0f / (1.0f + expf(-m));
             }
             __syncthreads();
-            // the weighted values: a thread owns outputs tid, tid + 256, ...
+            if constexpr (VEC) {
+                // the weighted values: a thread owns outputs 8 o .. 8 o + 7 for o = tid, tid + 256, ...
+                const int vchunks = V / 8, owners = H * vchunks;
 #pragma unroll
-            for (int a = 0; a < ACC; ++a) {
-                const int o = tid + kSigThreads * a;
-                if (o < HV) {
-                    const int h = o / V, e = o % V;
-                    const size_t col = (size_t)(h / per) * page_size;
-                    float s = acc[a];
+                for (int a = 0; a < NACC / 8; ++a) {
+                    const int o = tid + kSigThreads * a;
+                    if (o < owners) {
+                        const int h = o / vchunks, e = (o % vchunks) * 8;
+                        const size_t col = (size_t)(h / per) * page_size;
+#pragma unroll 8
+                        for (int jj = 0; jj < tn; ++jj) {
+                            float vv[8];
+                            load8(v_pool + ((size_t)rowbase[jj] + col) * (size_t)V + e, vv);
+                            const float w = wts[jj * H + h];
+#pragma unroll
+                            for (int x = 0; x < 8; ++x) acc[a * 8 + x] = fmaf(w, vv[x], acc[a * 8 + x]);
+                        }
+                    }
+                }
+            } else {
+                // the weighted values: a thread owns outputs tid, tid + 256, ...
+#pragma unroll
+                for (int a = 0; a < ACC; ++a) {
+                    const int o = tid + kSigThreads * a;
+                    if (o < HV) {
+                        const int h = o / V, e = o % V;
+                        const size_t col = (size_t)(h / per) * page_size;
+                        float s = acc[a];
 #pragma unroll 4
-                    for (int jj = 0; jj < tn; ++jj)
-                        s = fmaf(wts[jj * H + h], ldf(v_pool, ((size_t)rowbase[jj] + col) * (size_t)V + e), s);
-                    acc[a] = s;
+                        for (int jj = 0; jj < tn; ++jj)
+                            s = fmaf(wts[jj * H + h], ldf(v_pool, ((size_t)rowbase[jj] + col) * (size_t)V + e), s);
+                        acc[a] = s;
+                    }
                 }
             }
             __syncthreads();
         }
 #pragma unroll
-        for (int a = 0; a < ACC; ++a) total[a] += acc[a];
+        for (int a = 0; a < NACC; ++a) total[a] += acc[a];
     }
 #pragma unroll
-    for (int a = 0; a < ACC; ++a) {
-        const int o = tid + kSigThreads * a;
+    for (int a = 0; a < NACC; ++a) {
+        const int o = VEC ? (tid + kSigThreads * (a / 8)) * 8 + a % 8 : tid + kSigThreads * a;
         if (o < HV) {
             if (split) partial[((size_t)row * gridDim.y + blockIdx.y) * HV + o] = total[a];
             else stf(out, (size_t)row * HV + o, gate ? total[a] * gate[(size_t)row * H + o / V] : total[a]);
@@ -189,13 +270,13 @@ sigmoid_attention_merge_kernel(const float* __restrict__ partial, const int32_t*
     }
 }
 
-template <typename T, typename TQ, int PL, int ACC>
+template <typename T, typename TQ, int PL, int ACC, bool VEC>
 static int launch_sigmoid(const void* q, const void* k_pool, const void* v_pool, const int32_t* page_table, int table_stride,
                           const int32_t* row_slot, const int32_t* row_pos, const float* talk, const float* head_bias,
                           const float* gate, void* out, float* partial, int rows, int runs, int H, int G, int D, int V,
                           int page_size, int window, float scale, float slope_exp, cudaStream_t stream) {
     const size_t smem = (size_t)(H * D + H * H + 2 * H + 2 * kTileKeys * H) * sizeof(float) + kTileKeys * sizeof(int);
-    auto kernel = sigmoid_attention_kernel<T, TQ, PL, ACC>;
+    auto kernel = sigmoid_attention_kernel<T, TQ, PL, ACC, VEC>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -262,18 +343,29 @@ extern "C" int citlali_sigmoid_attention(const void* q, int q_dtype, const void*
         return kTooLarge;
     }
     const int HV = H * V;
-#define CITLALI_SIG(T, TQ, PL)                                                                                              \
+    const bool vec = D % 8 == 0 && V % 8 == 0 && ((uintptr_t)k_pool & 15u) == 0 && ((uintptr_t)v_pool & 15u) == 0;
+#define CITLALI_SIG(T, TQ, PL, VEC)                                                                                            \
     do {                                                                                                                    \
-        if (HV <= 256 * 2) return launch_sigmoid<T, TQ, PL, 2>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, talk, head_bias, gate, out, partial, rows, runs, H, G, D, V, page_size, window, scale, slope_exp, stream); \
-        if (HV <= 256 * 8) return launch_sigmoid<T, TQ, PL, 8>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, talk, head_bias, gate, out, partial, rows, runs, H, G, D, V, page_size, window, scale, slope_exp, stream); \
-        return launch_sigmoid<T, TQ, PL, 32>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, talk, head_bias, gate, out, partial, rows, runs, H, G, D, V, page_size, window, scale, slope_exp, stream); \
+        if (HV <= 256 * 2) return launch_sigmoid<T, TQ, PL, 2, VEC>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, talk, head_bias, gate, out, partial, rows, runs, H, G, D, V, page_size, window, scale, slope_exp, stream); \
+        if (HV <= 256 * 8) return launch_sigmoid<T, TQ, PL, 8, VEC>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, talk, head_bias, gate, out, partial, rows, runs, H, G, D, V, page_size, window, scale, slope_exp, stream); \
+        return launch_sigmoid<T, TQ, PL, 32, VEC>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, talk, head_bias, gate, out, partial, rows, runs, H, G, D, V, page_size, window, scale, slope_exp, stream); \
     } while (0)
+    if (q_dtype != cache_dtype) {
+        set_last_error("sigmoid_attention: queries and the cache must have one type");
+        return kBadShape;
+    }
     int rc = CITLALI_DISPATCH_FLOAT(cache_dtype, T, [&] {
-        return CITLALI_DISPATCH_FLOAT(q_dtype, TQ, [&]() -> int {
-            if (D <= 64) CITLALI_SIG(T, TQ, 2);
-            if (D <= 128) CITLALI_SIG(T, TQ, 4);
-            CITLALI_SIG(T, TQ, 8);
-        });
+        return [&]() -> int {
+            using TQ = T;
+            if (vec) {
+                if (D <= 64) CITLALI_SIG(T, TQ, 2, true);
+                if (D <= 128) CITLALI_SIG(T, TQ, 4, true);
+                CITLALI_SIG(T, TQ, 8, true);
+            }
+            if (D <= 64) CITLALI_SIG(T, TQ, 2, false);
+            if (D <= 128) CITLALI_SIG(T, TQ, 4, false);
+            CITLALI_SIG(T, TQ, 8, false);
+        }();
     });
 #undef CITLALI_SIG
     if (rc != 0 || runs == 1) return rc;
