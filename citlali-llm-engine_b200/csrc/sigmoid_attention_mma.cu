@@ -37,8 +37,20 @@ __host__ __device__ inline int padded_heads(int H) { return (H + 7) / 8 * 8; }
 
 inline size_t weights_smem(int H, int D) {
     const int hp = padded_heads(H);
-    return (size_t)H * kRows * (D * 2 + 16) + (size_t)kKeys * (D * 2 + 16) + (size_t)4 * H * 16 * kRows * sizeof(float) +
-           (size_t)(H * hp + hp + H) * sizeof(float);
+    return (size_t)H * kRows * (D * 2 + 16) + (size_t)2 * kKeys * (D * 2 + 16) + (size_t)4 * H * 16 * kRows * sizeof(float) +
+           (size_t)(2 * H * hp + hp + H) * sizeof(float);
+}
+
+// c += a * b on two floats at once.
+__device__ __forceinline__ void fma2(float2& c, const float2 a, const float2 b) {
+    asm("{\n .reg .b64 ra, rb, rc;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mov.b64 rc, {%0, %1};\n"
+        " fma.rn.f32x2 rc, ra, rb, rc;\n mov.b64 {%0, %1}, rc;\n}"
+        : "+f"(c.x), "+f"(c.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 // DK: head size / 16.
@@ -55,10 +67,10 @@ sigmoid_weights_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     extern __shared__ __align__(16) uint8_t smem[];
     const int hp = padded_heads(H), per = H / G;
     uint8_t* q_bytes = smem;                                               // [H, 8 rows, D (+8)]
-    uint8_t* k_bytes = q_bytes + (size_t)H * kRows * kRowBytes;            // [64 keys, D (+8)]
-    float* s_all = reinterpret_cast<float*>(k_bytes + kKeys * kRowBytes);  // [4 warps][H, 16 keys, 8 rows]
-    float* t_mix = s_all + 4 * H * 16 * kRows;                             // [H (g), hp (h)]: talk transposed, zero padded
-    float* t_bias = t_mix + H * hp;                                        // [hp]
+    uint8_t* k_bytes = q_bytes + (size_t)H * kRows * kRowBytes;            // [4 warps][2][16 keys, D (+8)]
+    float* s_all = reinterpret_cast<float*>(k_bytes + 2 * kKeys * kRowBytes);  // [4 warps][H, 16 keys, 8 rows]
+    float* t_mix = s_all + 4 * H * 16 * kRows;                             // [H (g), hp (h), 2]: talk transposed, each twice
+    float* t_bias = t_mix + 2 * H * hp;                                    // [hp], times -log2(e)
     float* t_slope = t_bias + hp;                                          // [H]
     const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(q_bytes), s_k = (uint32_t)__cvta_generic_to_shared(k_bytes);
 
@@ -86,57 +98,66 @@ sigmoid_weights_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     cp_async_commit();
     for (int i = tid; i < H * hp; i += 128) {
         const int g = i / hp, h = i % hp;
-        t_mix[i] = h < H ? (talk ? talk[h * H + g] : (h == g ? 1.0f : 0.0f)) : 0.0f;
+        t_mix[2 * i] = t_mix[2 * i + 1] = h < H ? (talk ? talk[h * H + g] : (h == g ? 1.0f : 0.0f)) : 0.0f;
     }
-    for (int i = tid; i < hp; i += 128) t_bias[i] = (head_bias && i < H) ? head_bias[i] : 0.0f;
+    for (int i = tid; i < hp; i += 128) t_bias[i] = (head_bias && i < H) ? -1.4426950408889634f * head_bias[i] : 0.0f;
     for (int i = tid; i < H; i += 128) t_slope[i] = slope_exp > 0.0f ? exp2f(-slope_exp * (float)(i + 1) / (float)H) : 0.0f;
 
     float* s_w = s_all + (size_t)warp * H * 16 * kRows;
     const int c_key = lane >> 2, c_row = (lane & 3) * 2;        // this lane's place in an accumulator tile
     const int m_key = lane >> 1, m_row = (lane & 1) * 4;        // and in the mix: a key and four rows
-    for (int t = t_begin; t < t_end; ++t) {
-        const int page = pages[t];
-        for (int kv = 0; kv < G; ++kv) {
-            __syncthreads();                                   // the last page's keys are no longer read
-            const size_t base = ((size_t)page * G + kv) * kKeys * D;
-            for (int c = tid; c < kKeys * kChunks; c += 128) {
-                const int r = c / kChunks, ch = c % kChunks;
-                cp_async16(s_k + r * kRowBytes + ch * 16, k_pool + base + (size_t)r * D + ch * 8);
-            }
-            cp_async_commit();
-            cp_async_wait<0>();
-            __syncthreads();
-            uint32_t kf[DK][4];
-            {
-                const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                const int cbyte = (lane >> 4) * 16;
+    // the keys come a (page, key/value head) at a time; each warp fetches its own 16 keys, the next ones while it works
+    const uint32_t my_k = s_k + warp * 2 * 16 * kRowBytes;
+    const int jobs = (t_end - t_begin) * G;
+    auto load_keys = [&](int n, int buf) {
+        const int t = t_begin + n / G, kv = n % G;
+        const size_t base = (((size_t)pages[t] * G + kv) * kKeys + warp * 16) * D;
+        for (int c = lane; c < 16 * kChunks; c += 32) {
+            const int r = c / kChunks, ch = c % kChunks;
+            cp_async16(my_k + (buf * 16 + r) * kRowBytes + ch * 16, k_pool + base + (size_t)r * D + ch * 8);
+        }
+    };
+    load_keys(0, 0);
+    cp_async_commit();
+    cp_async_wait<1>();                                        // the queries
+    __syncthreads();
+    for (int n = 0; n < jobs; ++n) {
+        const int t = t_begin + n / G, kv = n % G, buf = n & 1;
+        if (n + 1 < jobs) load_keys(n + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        uint32_t kf[DK][4];
+        {
+            const int r = buf * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            const int cbyte = (lane >> 4) * 16;
 #pragma unroll
-                for (int ks = 0; ks < DK; ++ks)
-                    ldmatrix_x4(s_k + r * kRowBytes + ks * 32 + cbyte, kf[ks][0], kf[ks][1], kf[ks][2], kf[ks][3]);
-            }
-            for (int hh = 0; hh < per; ++hh) {
-                const int g = kv * per + hh;
-                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                const uint32_t qb = s_q + (g * kRows + (lane & 7)) * kRowBytes + ((lane >> 3) & 1) * 16;
+            for (int ks = 0; ks < DK; ++ks)
+                ldmatrix_x4(my_k + r * kRowBytes + ks * 32 + cbyte, kf[ks][0], kf[ks][1], kf[ks][2], kf[ks][3]);
+        }
+        for (int hh = 0; hh < per; ++hh) {
+            const int g = kv * per + hh;
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const uint32_t qb = s_q + (g * kRows + (lane & 7)) * kRowBytes + ((lane >> 3) & 1) * 16;
 #pragma unroll
-                for (int ks = 0; ks < DK; ++ks) {
-                    uint32_t b0, b1;
-                    ldmatrix_x2(qb + ks * 32, b0, b1);
-                    mma_16816(acc, kf[ks][0], kf[ks][1], kf[ks][2], kf[ks][3], b0, b1);
-                }
-                const float slope = t_slope[g];
-                const int key = t * kKeys + warp * 16 + c_key, pos = past + q0 + c_row;
-                float2 lo2, hi2;
-                lo2.x = acc[0] * scale - slope * (float)(pos - key);
-                lo2.y = acc[1] * scale - slope * (float)(pos + 1 - key);
-                hi2.x = acc[2] * scale - slope * (float)(pos - key - 8);
-                hi2.y = acc[3] * scale - slope * (float)(pos + 1 - key - 8);
-                *reinterpret_cast<float2*>(s_w + (g * 16 + c_key) * kRows + c_row) = lo2;
-                *reinterpret_cast<float2*>(s_w + (g * 16 + c_key + 8) * kRows + c_row) = hi2;
+            for (int ks = 0; ks < DK; ++ks) {
+                uint32_t b0, b1;
+                ldmatrix_x2(qb + ks * 32, b0, b1);
+                mma_16816(acc, kf[ks][0], kf[ks][1], kf[ks][2], kf[ks][3], b0, b1);
             }
+            const float slope = t_slope[g];
+            const int key = t * kKeys + warp * 16 + c_key, pos = past + q0 + c_row;
+            float2 lo2, hi2;
+            lo2.x = acc[0] * scale - slope * (float)(pos - key);
+            lo2.y = acc[1] * scale - slope * (float)(pos + 1 - key);
+            hi2.x = acc[2] * scale - slope * (float)(pos - key - 8);
+            hi2.y = acc[3] * scale - slope * (float)(pos + 1 - key - 8);
+            *reinterpret_cast<float2*>(s_w + (g * 16 + c_key) * kRows + c_row) = lo2;
+            *reinterpret_cast<float2*>(s_w + (g * 16 + c_key + 8) * kRows + c_row) = hi2;
         }
         __syncwarp();
-        // the mix: this lane's key and four rows, eight output heads at a time
+        if (kv + 1 < G) continue;
+        // all heads' scores of this page are there.  The mix: this lane's key and four rows, eight output heads at a time
         const int key = t * kKeys + warp * 16 + m_key;
         bool visible[4];
 #pragma unroll
@@ -145,19 +166,24 @@ sigmoid_weights_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             visible[i] = r < n_new && key <= pos && (window <= 0 || key > pos - window);
         }
         const size_t col = (size_t)(t - tlo) * kKeys + warp * 16 + m_key;
+        __nv_bfloat16* w_at = W + ((size_t)group * ldc + col) * kRows + m_row;
+        const size_t w_head = (size_t)groups_total * ldc * kRows;
         for (int hc = 0; hc < hp; hc += 8) {
-            float m[8][4];
+            float2 m[8][2];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { m[j][0] = m[j][1] = m[j][2] = m[j][3] = 0.0f; }
+            for (int j = 0; j < 8; ++j) { m[j][0] = make_float2(0.0f, 0.0f); m[j][1] = make_float2(0.0f, 0.0f); }
+            const float* s_at = s_w + m_key * kRows + m_row;
+            const float* t_at = t_mix + 2 * hc;
+#pragma unroll 2
             for (int g = 0; g < H; ++g) {
-                const float4 s4 = *reinterpret_cast<const float4*>(s_w + (g * 16 + m_key) * kRows + m_row);
-                const float4 ta = *reinterpret_cast<const float4*>(t_mix + g * hp + hc);
-                const float4 tb = *reinterpret_cast<const float4*>(t_mix + g * hp + hc + 4);
-                const float tt[8] = {ta.x, ta.y, ta.z, ta.w, tb.x, tb.y, tb.z, tb.w};
+                const float4 s4 = *reinterpret_cast<const float4*>(s_at + g * 16 * kRows);
+                const float2 s01 = make_float2(s4.x, s4.y), s23 = make_float2(s4.z, s4.w);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    m[j][0] = fmaf(tt[j], s4.x, m[j][0]); m[j][1] = fmaf(tt[j], s4.y, m[j][1]);
-                    m[j][2] = fmaf(tt[j], s4.z, m[j][2]); m[j][3] = fmaf(tt[j], s4.w, m[j][3]);
+                for (int j = 0; j < 8; j += 2) {
+                    const float4 tt = *reinterpret_cast<const float4*>(t_at + (size_t)g * 2 * hp + 2 * j);
+                    const float2 ta = make_float2(tt.x, tt.y), tb = make_float2(tt.z, tt.w);
+                    fma2(m[j][0], ta, s01); fma2(m[j][1], ta, s23);
+                    fma2(m[j + 1][0], tb, s01); fma2(m[j + 1][1], tb, s23);
                 }
             }
 #pragma unroll
@@ -165,18 +191,21 @@ sigmoid_weights_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 const int h = hc + j;
                 if (h < H) {
                     const float b = t_bias[h];
+                    const float x[4] = {m[j][0].x, m[j][0].y, m[j][1].x, m[j][1].y};
                     float w[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) w[i] = visible[i] ? __fdividef(1.0f, 1.0f + __expf(-(m[j][i] + b))) : 0.0f;
+                    for (int i = 0; i < 4; ++i)          // 1 / (1 + 2^(-(m + bias) log2 e))
+                        w[i] = visible[i] ? fast_rcp(1.0f + fast_exp2(fmaf(x[i], -1.4426950408889634f, b))) : 0.0f;
                     uint2 packed;
                     packed.x = pack_bf16(w[0], w[1]);
                     packed.y = pack_bf16(w[2], w[3]);
-                    *reinterpret_cast<uint2*>(W + (((size_t)h * groups_total + group) * ldc + col) * kRows + m_row) = packed;
+                    *reinterpret_cast<uint2*>(w_at + (size_t)h * w_head) = packed;
                 }
             }
         }
         __syncwarp();
     }
+    cp_async_wait<0>();
 }
 
 // VK: value size / 16.
