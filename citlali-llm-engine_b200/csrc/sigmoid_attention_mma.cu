@@ -1,11 +1,11 @@
 // Sigmoid attention of runs of new tokens on the tensor cores (bfloat16 cache, pages of 64 keys), in two kernels, because
 // a head's weight needs every head's score and no block can keep the outputs of all heads:
 //
-//   sigmoid_weights  a block takes 8 consecutive rows of a sequence, ALL heads, and a run of key pages.  Per page and
-//                    key/value head the page's keys go to shared memory; each of the four warps owns 16 of the 64 keys and
-//                    computes K Q_g^T for the heads g of that key/value head with mma.sync m16n8k16 (keys are M, the 8 rows
+//   sigmoid_weights  a block takes 8 consecutive rows of a sequence, ALL heads, and a run of key pages.  Two of its eight warps
+//                    share 16 of a page's 64 keys: each fetches them per key/value head (cp.async, straight on to
+//                    registers), computes K Q_g^T for its half of the heads g with mma.sync m16n8k16 (keys are M, the 8 rows
 //                    are N), takes the scale and the distance term in float32 and leaves s_g in shared memory.  When all
-//                    heads are there, the warp mixes them on the CUDA cores, m_h = sum_g talk[h, g] s_g + head_bias[h],
+//                    heads are there, the two warps mix them on the CUDA cores, eight output heads at a time, m_h = sum_g talk[h, g] s_g + head_bias[h],
 //                    takes the sigmoid (0 where the key is not visible) and writes the weights in bfloat16 to
 //                    W [head, group of 8 rows, column, 8 rows]; column 0 is the first key of the first page that the
 //                    16 rows around the group can see.
@@ -43,9 +43,8 @@ inline size_t weights_smem(int H, int D) {
 
 // c += a * b on two floats at once.
 __device__ __forceinline__ void fma2(float2& c, const float2 a, const float2 b) {
-    asm("{\n .reg .b64 ra, rb, rc;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mov.b64 rc, {%0, %1};\n"
-        " fma.rn.f32x2 rc, ra, rb, rc;\n mov.b64 {%0, %1}, rc;\n}"
-        : "+f"(c.x), "+f"(c.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    c.x = fmaf(a.x, b.x, c.x);
+    c.y = fmaf(a.y, b.y, c.y);
 }
 __device__ __forceinline__ float fast_rcp(float x) {
     float y;
@@ -55,7 +54,7 @@ __device__ __forceinline__ float fast_rcp(float x) {
 
 // DK: head size / 16.
 template <int DK>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256, 2)
 sigmoid_weights_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                        const int32_t* __restrict__ page_table, int table_stride, const int32_t* __restrict__ seq_start,
                        const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_past,
@@ -89,92 +88,107 @@ sigmoid_weights_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const int32_t* pages = page_table + (size_t)seq_slot[seq] * table_stride;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    for (int c = tid; c < H * kRows * kChunks; c += 128) {
+    for (int c = tid; c < H * kRows * kChunks; c += 256) {
         const int ch = c % kChunks, r = (c / kChunks) % kRows, h = c / (kChunks * kRows);
         const int at = (h * kRows + r) * kRowBytes + ch * 16;
         if (q0 + r < n_new) cp_async16(s_q + at, q + ((size_t)(row0 + q0 + r) * H + h) * D + ch * 8);
         else *reinterpret_cast<uint4*>(q_bytes + at) = make_uint4(0, 0, 0, 0);
     }
     cp_async_commit();
-    for (int i = tid; i < H * hp; i += 128) {
+    for (int i = tid; i < H * hp; i += 256) {
         const int g = i / hp, h = i % hp;
         t_mix[2 * i] = t_mix[2 * i + 1] = h < H ? (talk ? talk[h * H + g] : (h == g ? 1.0f : 0.0f)) : 0.0f;
     }
-    for (int i = tid; i < hp; i += 128) t_bias[i] = (head_bias && i < H) ? -1.4426950408889634f * head_bias[i] : 0.0f;
-    for (int i = tid; i < H; i += 128) t_slope[i] = slope_exp > 0.0f ? exp2f(-slope_exp * (float)(i + 1) / (float)H) : 0.0f;
+    for (int i = tid; i < hp; i += 256) t_bias[i] = (head_bias && i < H) ? -1.4426950408889634f * head_bias[i] : 0.0f;
+    for (int i = tid; i < H; i += 256) t_slope[i] = slope_exp > 0.0f ? exp2f(-slope_exp * (float)(i + 1) / (float)H) : 0.0f;
 
-    float* s_w = s_all + (size_t)warp * H * 16 * kRows;
+    // Two warps share 16 of the page's keys: each computes the scores of its half of the heads (split between key/value
+    // heads where there are several), then each mixes every other run of eight output heads.
+    const int slice = warp & 3, half = warp >> 2;
+    const int h_mid = G >= 2 ? (G + 1) / 2 * per : (H + 1) / 2;
+    const int h_lo = half ? h_mid : 0, h_hi = half ? H : h_mid;
+    const int kv_lo = h_lo / per, nkv = h_hi > h_lo ? (h_hi - 1) / per - kv_lo + 1 : 0;
+    const int tiles = t_end - t_begin, jobs = tiles * nkv;
+    float* s_w = s_all + (size_t)slice * H * 16 * kRows;
     const int c_key = lane >> 2, c_row = (lane & 3) * 2;        // this lane's place in an accumulator tile
     const int m_key = lane >> 1, m_row = (lane & 1) * 4;        // and in the mix: a key and four rows
-    // the keys come a (page, key/value head) at a time; each warp fetches its own 16 keys, the next ones while it works
-    const uint32_t my_k = s_k + warp * 2 * 16 * kRowBytes;
-    const int jobs = (t_end - t_begin) * G;
-    auto load_keys = [&](int n, int buf) {
-        const int t = t_begin + n / G, kv = n % G;
-        const size_t base = (((size_t)pages[t] * G + kv) * kKeys + warp * 16) * D;
+    // a warp fetches its 16 keys of a (page, key/value head) into its own buffer; they leave it for registers at once, so the
+    // next ones are fetched while the warp works
+    const uint32_t my_k = s_k + warp * 16 * kRowBytes;
+    auto load_keys = [&](int n) {
+        const int t = t_begin + n / nkv, kv = kv_lo + n % nkv;
+        const size_t base = (((size_t)pages[t] * G + kv) * kKeys + slice * 16) * D;
         for (int c = lane; c < 16 * kChunks; c += 32) {
             const int r = c / kChunks, ch = c % kChunks;
-            cp_async16(my_k + (buf * 16 + r) * kRowBytes + ch * 16, k_pool + base + (size_t)r * D + ch * 8);
+            cp_async16(my_k + r * kRowBytes + ch * 16, k_pool + base + (size_t)r * D + ch * 8);
         }
     };
-    load_keys(0, 0);
+    auto pair_barrier = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + slice) : "memory"); };
+    if (jobs > 0) load_keys(0);
     cp_async_commit();
     cp_async_wait<1>();                                        // the queries
     __syncthreads();
-    for (int n = 0; n < jobs; ++n) {
-        const int t = t_begin + n / G, kv = n % G, buf = n & 1;
-        if (n + 1 < jobs) load_keys(n + 1, buf ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncwarp();
-        uint32_t kf[DK][4];
-        {
-            const int r = buf * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-            const int cbyte = (lane >> 4) * 16;
+    int n = 0;
+    for (int ti = 0; ti < tiles; ++ti) {
+        const int t = t_begin + ti;
+        // distances of this lane's four places in an accumulator tile (the same for every head)
+        const int key0 = t * kKeys + slice * 16 + c_key, pos0 = past + q0 + c_row;
+        const float d00 = (float)(pos0 - key0), d01 = d00 + 1.0f, d10 = d00 - 8.0f, d11 = d00 - 7.0f;
+        for (int k = 0; k < nkv; ++k, ++n) {
+            const int kv = kv_lo + k;
+            cp_async_wait<0>();
+            __syncwarp();
+            uint32_t kf[DK][4];
+            {
+                const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int cbyte = (lane >> 4) * 16;
 #pragma unroll
-            for (int ks = 0; ks < DK; ++ks)
-                ldmatrix_x4(my_k + r * kRowBytes + ks * 32 + cbyte, kf[ks][0], kf[ks][1], kf[ks][2], kf[ks][3]);
-        }
-        for (int hh = 0; hh < per; ++hh) {
-            const int g = kv * per + hh;
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const uint32_t qb = s_q + (g * kRows + (lane & 7)) * kRowBytes + ((lane >> 3) & 1) * 16;
-#pragma unroll
-            for (int ks = 0; ks < DK; ++ks) {
-                uint32_t b0, b1;
-                ldmatrix_x2(qb + ks * 32, b0, b1);
-                mma_16816(acc, kf[ks][0], kf[ks][1], kf[ks][2], kf[ks][3], b0, b1);
+                for (int ks = 0; ks < DK; ++ks)
+                    ldmatrix_x4(my_k + r * kRowBytes + ks * 32 + cbyte, kf[ks][0], kf[ks][1], kf[ks][2], kf[ks][3]);
             }
-            const float slope = t_slope[g];
-            const int key = t * kKeys + warp * 16 + c_key, pos = past + q0 + c_row;
-            float2 lo2, hi2;
-            lo2.x = acc[0] * scale - slope * (float)(pos - key);
-            lo2.y = acc[1] * scale - slope * (float)(pos + 1 - key);
-            hi2.x = acc[2] * scale - slope * (float)(pos - key - 8);
-            hi2.y = acc[3] * scale - slope * (float)(pos + 1 - key - 8);
-            *reinterpret_cast<float2*>(s_w + (g * 16 + c_key) * kRows + c_row) = lo2;
-            *reinterpret_cast<float2*>(s_w + (g * 16 + c_key + 8) * kRows + c_row) = hi2;
+            __syncwarp();
+            if (n + 1 < jobs) load_keys(n + 1);
+            cp_async_commit();
+            const int g_end = min(h_hi, (kv + 1) * per);
+            for (int g = max(h_lo, kv * per); g < g_end; ++g) {
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, odd[4] = {0.0f, 0.0f, 0.0f, 0.0f};      // two chains of MMAs
+                const uint32_t qb = s_q + (g * kRows + (lane & 7)) * kRowBytes + ((lane >> 3) & 1) * 16;
+#pragma unroll
+                for (int ks = 0; ks < DK; ++ks) {
+                    uint32_t b0, b1;
+                    ldmatrix_x2(qb + ks * 32, b0, b1);
+                    if (ks & 1) mma_16816(odd, kf[ks][0], kf[ks][1], kf[ks][2], kf[ks][3], b0, b1);
+                    else mma_16816(acc, kf[ks][0], kf[ks][1], kf[ks][2], kf[ks][3], b0, b1);
+                }
+                const float slope = t_slope[g];
+                float2 lo2, hi2;
+                lo2.x = (acc[0] + odd[0]) * scale - slope * d00;
+                lo2.y = (acc[1] + odd[1]) * scale - slope * d01;
+                hi2.x = (acc[2] + odd[2]) * scale - slope * d10;
+                hi2.y = (acc[3] + odd[3]) * scale - slope * d11;
+                *reinterpret_cast<float2*>(s_w + (g * 16 + c_key) * kRows + c_row) = lo2;
+                *reinterpret_cast<float2*>(s_w + (g * 16 + c_key + 8) * kRows + c_row) = hi2;
+            }
         }
-        __syncwarp();
-        if (kv + 1 < G) continue;
+        pair_barrier();
         // all heads' scores of this page are there.  The mix: this lane's key and four rows, eight output heads at a time
-        const int key = t * kKeys + warp * 16 + m_key;
+        const int key = t * kKeys + slice * 16 + m_key;
         bool visible[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int r = q0 + m_row + i, pos = past + r;
             visible[i] = r < n_new && key <= pos && (window <= 0 || key > pos - window);
         }
-        const size_t col = (size_t)(t - tlo) * kKeys + warp * 16 + m_key;
+        const size_t col = (size_t)(t - tlo) * kKeys + slice * 16 + m_key;
         __nv_bfloat16* w_at = W + ((size_t)group * ldc + col) * kRows + m_row;
         const size_t w_head = (size_t)groups_total * ldc * kRows;
-        for (int hc = 0; hc < hp; hc += 8) {
+        for (int hc = half * 8; hc < hp; hc += 16) {
             float2 m[8][2];
 #pragma unroll
             for (int j = 0; j < 8; ++j) { m[j][0] = make_float2(0.0f, 0.0f); m[j][1] = make_float2(0.0f, 0.0f); }
             const float* s_at = s_w + m_key * kRows + m_row;
             const float* t_at = t_mix + 2 * hc;
-#pragma unroll 2
+#pragma unroll 4
             for (int g = 0; g < H; ++g) {
                 const float4 s4 = *reinterpret_cast<const float4*>(s_at + g * 16 * kRows);
                 const float2 s01 = make_float2(s4.x, s4.y), s23 = make_float2(s4.z, s4.w);
@@ -189,21 +203,21 @@ sigmoid_weights_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const int h = hc + j;
-                if (h < H) {
-                    const float b = t_bias[h];
-                    const float x[4] = {m[j][0].x, m[j][0].y, m[j][1].x, m[j][1].y};
-                    float w[4];
+                const float b = t_bias[h];
+                const float x[4] = {m[j][0].x, m[j][0].y, m[j][1].x, m[j][1].y};
+                float w[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)          // 1 / (1 + 2^(-(m + bias) log2 e))
-                        w[i] = visible[i] ? fast_rcp(1.0f + fast_exp2(fmaf(x[i], -1.4426950408889634f, b))) : 0.0f;
-                    uint2 packed;
-                    packed.x = pack_bf16(w[0], w[1]);
-                    packed.y = pack_bf16(w[2], w[3]);
-                    *reinterpret_cast<uint2*>(w_at + (size_t)h * w_head) = packed;
+                for (int i = 0; i < 4; ++i) {            // 1 / (1 + 2^(-(m + bias) log2 e)), 0 for a key that is not visible
+                    w[i] = fast_rcp(1.0f + fast_exp2(fmaf(x[i], -1.4426950408889634f, b)));
+                    w[i] = visible[i] ? w[i] : 0.0f;
                 }
+                uint2 packed;
+                packed.x = pack_bf16(w[0], w[1]);
+                packed.y = pack_bf16(w[2], w[3]);
+                if (h < H) *reinterpret_cast<uint2*>(w_at + (size_t)h * w_head) = packed;
             }
         }
-        __syncwarp();
+        pair_barrier();                                        // the scores are read before the next page's are written
     }
     cp_async_wait<0>();
 }
@@ -319,7 +333,7 @@ static int launch_weights(dim3 grid, size_t smem, cudaStream_t stream, const voi
     auto kernel = sigmoid_weights_kernel<DK>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    launch_kernel(kernel, grid, 128, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, page_table, table_stride,
+    launch_kernel(kernel, grid, 256, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, page_table, table_stride,
                   seq_start, seq_slot, seq_past, talk, head_bias, (__nv_bfloat16*)W, ldc, groups_total, H, G, window, scale,
                   slope_exp);
     return CITLALI_LAUNCH_CHECK();
