@@ -14,17 +14,47 @@
 
 namespace citlali {
 
-template <typename TZ, typename TO>
+__device__ __forceinline__ float xielu(float u, float ap, float an) {
+    return u > 0.0f ? fmaf(ap * u, u, 0.5f * u) : fmaf(an, expm1f(u) - u, 0.5f * u);
+}
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                       __uint_as_float(u.y & 0xffff0000u));
+}
+__device__ __forceinline__ void store4(float* p, const float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&lo);
+    u.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+// A block row (and a share of its columns); VEC: four neighbouring columns a thread (n a multiple of four, 16-byte rows).
+template <typename TZ, typename TO, bool VEC>
 __global__ void __launch_bounds__(256)
-bias_xielu_kernel(const TZ* __restrict__ z, const float* __restrict__ bias, float ap, float an, TO* __restrict__ out, size_t total,
-                  int n) {
+bias_xielu_kernel(const TZ* __restrict__ z, const float* __restrict__ bias, float ap, float an, TO* __restrict__ out, int n) {
     dependents_may_launch();
     wait_for_predecessor();
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        float u = ldf(z, i);
-        if (bias) u += bias[i % n];
-        const float r = u > 0.0f ? fmaf(ap * u, u, 0.5f * u) : fmaf(an, expm1f(u) - u, 0.5f * u);
-        stf(out, i, r);
+    const TZ* zr = z + (size_t)blockIdx.x * n;
+    TO* o = out + (size_t)blockIdx.x * n;
+    if constexpr (VEC) {
+        for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < n; c += gridDim.y * blockDim.x * 4) {
+            float4 u = load4(zr + c);
+            if (bias) {
+                const float4 b = *reinterpret_cast<const float4*>(bias + c);
+                u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+            }
+            store4(o + c, make_float4(xielu(u.x, ap, an), xielu(u.y, ap, an), xielu(u.z, ap, an), xielu(u.w, ap, an)));
+        }
+    } else {
+        for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n; c += gridDim.y * blockDim.x) {
+            float u = ldf(zr, c);
+            if (bias) u += bias[c];
+            stf(o, c, xielu(u, ap, an));
+        }
     }
 }
 
@@ -78,12 +108,14 @@ using namespace citlali;
 extern "C" int citlali_bias_xielu(const void* z, int z_dtype, const float* bias, float ap, float an, void* out, int out_dtype,
                                   int rows, int n, cudaStream_t stream) {
     if (rows <= 0 || n <= 0) return 0;
-    const size_t total = (size_t)rows * n;
-    const size_t blocks = (total + 255) / 256;
-    const int grid = (int)(blocks < 16384 ? blocks : 16384);
+    const bool vec = n % 4 == 0 && (((uintptr_t)z | (uintptr_t)out | (uintptr_t)bias) & 15u) == 0;
+    const int per_block = vec ? 1024 : 256;
+    const int by = (n + per_block - 1) / per_block;
+    const dim3 grid(rows, by < 64 ? by : 64);
     return CITLALI_DISPATCH_FLOAT(z_dtype, TZ, [&] {
         return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
-            launch_kernel(bias_xielu_kernel<TZ, TO>, grid, 256, 0, stream, (const TZ*)z, bias, ap, an, (TO*)out, total, n);
+            if (vec) launch_kernel(bias_xielu_kernel<TZ, TO, true>, grid, 256, 0, stream, (const TZ*)z, bias, ap, an, (TO*)out, n);
+            else launch_kernel(bias_xielu_kernel<TZ, TO, false>, grid, 256, 0, stream, (const TZ*)z, bias, ap, an, (TO*)out, n);
             return CITLALI_LAUNCH_CHECK();
         });
     });

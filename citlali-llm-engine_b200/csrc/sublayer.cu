@@ -225,6 +225,95 @@ layer_norm_chain_kernel(const float* __restrict__ y, const float* __restrict__ i
         stf(out2, (size_t)row * hidden + i, (row_s[i] - mean2) * inv2 * g2[i] + (b2 ? b2[i] : 0.0f));
 }
 
+__device__ __forceinline__ void store4(float* p, size_t i, const float4 v) { *reinterpret_cast<float4*>(p + i) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, size_t i, const float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&lo);
+    u.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p + i) = u;
+}
+
+// The same chain for rows whose length is a multiple of four and at most 4096 NV: a thread keeps NV runs of four
+// elements in registers through all passes (16-byte loads and stores, no copy of the row in shared memory).  The order of
+// the sums follows the row's length alone.
+template <typename TE, int NV>
+__global__ void __launch_bounds__(1024)
+layer_norm_chain_vec_kernel(const float* __restrict__ y, const float* __restrict__ in_bias, const float* __restrict__ g1,
+                            const float* __restrict__ b1, float* __restrict__ x, TE* __restrict__ emit,
+                            const float* __restrict__ g2, const float* __restrict__ b2, TE* __restrict__ out2, int hidden,
+                            float eps1, float eps2) {
+    __shared__ float scratch[32];
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int nvec = hidden / 4;
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float4 v[NV];
+    float s = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
+        const int i = c * blockDim.x + threadIdx.x;
+        v[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < nvec) {
+            v[c] = *reinterpret_cast<const float4*>(y + base + 4 * i);
+            if (in_bias) {
+                const float4 b = *reinterpret_cast<const float4*>(in_bias + 4 * i);
+                v[c].x += b.x; v[c].y += b.y; v[c].z += b.z; v[c].w += b.w;
+            }
+            s += (v[c].x + v[c].y) + (v[c].z + v[c].w);
+        }
+    }
+    const float mean = block_sum(s, scratch) / (float)hidden;
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
+        if (c * blockDim.x + threadIdx.x < nvec) {
+            const float dx = v[c].x - mean, dy = v[c].y - mean, dz = v[c].z - mean, dw = v[c].w - mean;
+            ss += fmaf(dx, dx, dy * dy) + fmaf(dz, dz, dw * dw);
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps1);
+    float s2 = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
+        const int i = c * blockDim.x + threadIdx.x;
+        if (i < nvec) {
+            const float4 g = *reinterpret_cast<const float4*>(g1 + 4 * i);
+            const float4 b = b1 ? *reinterpret_cast<const float4*>(b1 + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            float4 r = *reinterpret_cast<const float4*>(x + base + 4 * i);
+            r.x += (v[c].x - mean) * inv * g.x + b.x;
+            r.y += (v[c].y - mean) * inv * g.y + b.y;
+            r.z += (v[c].z - mean) * inv * g.z + b.z;
+            r.w += (v[c].w - mean) * inv * g.w + b.w;
+            *reinterpret_cast<float4*>(x + base + 4 * i) = r;
+            if (emit) store4(emit, base + 4 * i, r);
+            v[c] = r;
+            s2 += (r.x + r.y) + (r.z + r.w);
+        }
+    }
+    if (g2 == nullptr) return;
+    const float mean2 = block_sum(s2, scratch) / (float)hidden;
+    float ss2 = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
+        if (c * blockDim.x + threadIdx.x < nvec) {
+            const float dx = v[c].x - mean2, dy = v[c].y - mean2, dz = v[c].z - mean2, dw = v[c].w - mean2;
+            ss2 += fmaf(dx, dx, dy * dy) + fmaf(dz, dz, dw * dw);
+        }
+    }
+    const float inv2 = 1.0f / sqrtf(block_sum(ss2, scratch) / (float)hidden + eps2);
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
+        const int i = c * blockDim.x + threadIdx.x;
+        if (i < nvec) {
+            const float4 g = *reinterpret_cast<const float4*>(g2 + 4 * i);
+            const float4 b = b2 ? *reinterpret_cast<const float4*>(b2 + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            store4(out2, base + 4 * i, make_float4((v[c].x - mean2) * inv2 * g.x + b.x, (v[c].y - mean2) * inv2 * g.y + b.y,
+                                                   (v[c].z - mean2) * inv2 * g.z + b.z, (v[c].w - mean2) * inv2 * g.w + b.w));
+        }
+    }
+}
+
 static int grid_for(size_t n) {
     const size_t blocks = (n + 255) / 256;
     return (int)(blocks < 8192 ? (blocks ? blocks : 1) : 8192);
@@ -319,6 +408,17 @@ extern "C" int citlali_layer_norm_chain(const float* y, const float* in_bias, co
     }
     int threads = ((hidden / 4 + 31) / 32) * 32;             // follows the row's length alone: one order of sums a row
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+    const uintptr_t together = (uintptr_t)y | (uintptr_t)in_bias | (uintptr_t)g1 | (uintptr_t)b1 | (uintptr_t)x | (uintptr_t)emit |
+                               (uintptr_t)g2 | (uintptr_t)b2 | (uintptr_t)out2;
+    if (hidden % 4 == 0 && hidden <= 4 * 4096 && (together & 15u) == 0) {
+        const int nv = (hidden / 4 + threads - 1) / threads;             // 1, 2, 3 or 4 runs of four elements a thread
+        return CITLALI_DISPATCH_FLOAT(out_dtype, TE, [&] {
+            if (nv <= 1) launch_kernel(layer_norm_chain_vec_kernel<TE, 1>, rows, threads, 0, stream, y, in_bias, g1, b1, x, (TE*)emit, g2, b2, (TE*)out2, hidden, eps1, eps2);
+            else if (nv <= 2) launch_kernel(layer_norm_chain_vec_kernel<TE, 2>, rows, threads, 0, stream, y, in_bias, g1, b1, x, (TE*)emit, g2, b2, (TE*)out2, hidden, eps1, eps2);
+            else launch_kernel(layer_norm_chain_vec_kernel<TE, 4>, rows, threads, 0, stream, y, in_bias, g1, b1, x, (TE*)emit, g2, b2, (TE*)out2, hidden, eps1, eps2);
+            return CITLALI_LAUNCH_CHECK();
+        });
+    }
     return CITLALI_DISPATCH_FLOAT(out_dtype, TE, [&] {
         auto kernel = layer_norm_chain_kernel<TE>;
         if (smem > 48 * 1024) {

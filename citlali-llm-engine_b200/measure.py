@@ -93,7 +93,8 @@ class KernelTimer:
 
     SKIP = {"lib", "launch_count", "sm_count", "zero_counters", "attention", "gemm_tc_plan", "gemm_tc_accepts",
             "gemm_tc_pair_plan", "gemm_tc_runs_on_pairs", "gemm_tc_is_small_form", "gemm_tc_set_pair_rows",
-            "attention_steps_from_device", "wait_selftest"}
+            "attention_steps_from_device", "wait_selftest", "sigmoid_attention_mma_supports",
+            "sigmoid_attention_mma_scratch_bytes", "sigmoid_attention_run_keys"}
 
     def __init__(self):
         self.records: List[tuple] = []
