@@ -336,7 +336,7 @@ def test_each_position_term_alone(dtype):
 
 # ---- norms ------------------------------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("hidden", [60, 256, 1000, 4100])
+@pytest.mark.parametrize("hidden", [60, 75, 256, 1000, 4100, 4102, 9000])   # 75, 4102: no multiple of four (one element a thread)
 def test_layer_norm_with_bias_and_the_chain(hidden):
     g = torch.Generator().manual_seed(hidden)
     rnd = lambda *shape: torch.randn(*shape, generator=g)
@@ -366,7 +366,7 @@ def test_layer_norm_with_bias_and_the_chain(hidden):
 # ---- feed-forwards ------------------------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden,ff,act", [(64, 96, (0.3, -0.4)), (60, 100, (-2.0, 1.5)), (128, 512, (0.0, 0.0))])
+@pytest.mark.parametrize("hidden,ff,act", [(64, 96, (0.3, -0.4)), (60, 100, (-2.0, 1.5)), (128, 512, (0.0, 0.0)), (64, 90, (0.5, 0.2))])
 def test_xielu_feed_forward(hidden, ff, act, dtype):
     part = build_part("feed_forward", PartSpec("xielu", {"hidden_size": hidden, "intermediate_size": ff}, "f"))
     w = draw(part.tensor_specs(), ff)
