@@ -5,7 +5,7 @@
     results = session.generate([[1, 2, 3], [4, 5]], cb.GenerationOptions(max_new_tokens=16))
 """
 from .errors import CitlaliError, require
-from .config import (QwenConfig, LanizenConfig, GidiraxConfig, ModelSpec, LayerSpec, PartSpec, ScheduleStep, config_from_dict,
+from .config import (QwenConfig, LanizenConfig, GidiraxConfig, SobunexConfig, PivavikConfig, ModelSpec, LayerSpec, PartSpec, ScheduleStep, config_from_dict,
                      config_from_model_dir, register_architecture, registered_architectures,
                      unregister_architecture)
 from .weights import (SafetensorsFile, TensorSpec, WeightHandle, WeightLoader, write_random_model,

@@ -6,6 +6,8 @@ from .gidirax import GidiraxConfig
 from . import gidirax as _gidirax
 from .sobunex import SobunexConfig
 from . import sobunex as _sobunex
+from .pivavik import PivavikConfig
+from . import pivavik as _pivavik
 from .registry import (config_class_for, config_from_dict, config_from_model_dir,
                        register_architecture, registered_architectures, unregister_architecture)
 
@@ -13,3 +15,4 @@ register_architecture(ARCHITECTURE, QwenConfig)
 register_architecture(_lanizen.ARCHITECTURE, LanizenConfig)
 register_architecture(_gidirax.ARCHITECTURE, GidiraxConfig)
 register_architecture(_sobunex.ARCHITECTURE, SobunexConfig)
+register_architecture(_pivavik.ARCHITECTURE, PivavikConfig)

@@ -66,6 +66,8 @@ class ModelSpec:
     # None: one residual stream [rows, hidden].  A number S: the residual is S streams [S, rows, hidden] that all start
     # as the embedding's rows and are summed before the last norm; every layer's block must be one that takes streams.
     residual_streams: Optional[int] = None
+    embedding_norm: Optional[PartSpec] = None  # a norm the embedding's rows pass before the first layer (32-bit in and out)
+    logit_softcap: Optional[float] = None      # the logits become cap tanh(logits / cap), after the scale if there is one
 
     def validate(self):
         from ..errors import require

@@ -7,8 +7,12 @@
 //                     columns are, expert after expert, gate and up alternating in runs:
 //                         kind 0:  silu(g) u
 //                         kind 1:  g' = min(g, limit), u' = clamp(u, -limit, limit);  g' sigmoid(alpha g') (u' + 1)
+//                         kind 2:  gelu_tanh(g) u,  gelu_tanh(z) = z / 2 (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+//                     after an optional bias on gate and up,
 //                     times the row's weight for the expert (zero: the expert's activations are zeros and its inputs are
-//                     not read).  The expert for every row comes last, has a width, run and limit of its own and weight 1.
+//                     not read), or, with weight_input, of the activation of gate and up each times that weight (the
+//                     expert applied to its weighted input).  The expert for every row comes last, has a width, run and
+//                     limit of its own and weight 1.
 #include "api.h"
 #include "common.cuh"
 
@@ -68,6 +72,7 @@ add_row_bias_kernel(float* __restrict__ y, const float* __restrict__ bias, size_
 
 __device__ __forceinline__ float gated(float g, float u, int kind, float limit, float alpha) {
     if (kind == 0) return g / (1.0f + expf(-g)) * u;
+    if (kind == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * g * g, g, g))) * u;
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
@@ -76,7 +81,8 @@ __device__ __forceinline__ float gated(float g, float u, int kind, float limit, 
 template <typename TZ, typename TO>
 __global__ void __launch_bounds__(256)
 expert_gate_kernel(const TZ* __restrict__ gu, const float* __restrict__ weights, TO* __restrict__ act, int E, int ff, int run,
-                   int kind, float limit, float alpha, int tail_ff, int tail_run, float tail_limit) {
+                   int kind, float limit, float alpha, int tail_ff, int tail_run, float tail_limit,
+                   const float* __restrict__ bias, int weight_input) {
     dependents_may_launch();
     wait_for_predecessor();
     const int row = blockIdx.x;
@@ -90,12 +96,16 @@ expert_gate_kernel(const TZ* __restrict__ gu, const float* __restrict__ weights,
             const float w = weights[(size_t)row * E + e];
             if (w != 0.0f) {
                 const size_t at = (size_t)e * 2 * ff + (size_t)(j / run) * 2 * run + j % run;
-                r = w * gated(ldf(in, at), ldf(in, at + run), kind, limit, alpha);
+                float g = ldf(in, at), u = ldf(in, at + run);
+                if (bias) { g += bias[at]; u += bias[at + run]; }
+                r = weight_input ? gated(w * g, w * u, kind, limit, alpha) : w * gated(g, u, kind, limit, alpha);
             }
         } else {
             const int j = i - routed;
             const size_t at = (size_t)2 * routed + (size_t)(j / tail_run) * 2 * tail_run + j % tail_run;
-            r = gated(ldf(in, at), ldf(in, at + tail_run), kind, tail_limit, alpha);
+            float g = ldf(in, at), u = ldf(in, at + tail_run);
+            if (bias) { g += bias[at]; u += bias[at + tail_run]; }
+            r = gated(g, u, kind, tail_limit, alpha);
         }
         stf(o, i, r);
     }
@@ -131,10 +141,10 @@ extern "C" int citlali_add_row_bias(float* y, const float* bias, int rows, int n
 
 extern "C" int citlali_expert_gate(const void* gate_up, int in_dtype, const float* weights, void* act, int act_dtype, int rows,
                                    int E, int ff, int run, int kind, float limit, float alpha, int tail_ff, int tail_run,
-                                   float tail_limit, cudaStream_t stream) {
+                                   float tail_limit, const float* bias, int weight_input, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (E < 0 || ff < 0 || tail_ff < 0 || (E > 0 && (ff <= 0 || run <= 0 || ff % run != 0 || weights == nullptr)) ||
-        (tail_ff > 0 && (tail_run <= 0 || tail_ff % tail_run != 0)) || (kind != 0 && kind != 1) || E * ff + tail_ff <= 0) {
+        (tail_ff > 0 && (tail_run <= 0 || tail_ff % tail_run != 0)) || kind < 0 || kind > 2 || E * ff + tail_ff <= 0) {
         set_last_error("expert_gate: %d experts of %d in runs of %d, an expert for all of %d in runs of %d, kind %d", E, ff, run,
                        tail_ff, tail_run, kind);
         return kBadShape;
@@ -145,7 +155,7 @@ extern "C" int citlali_expert_gate(const void* gate_up, int in_dtype, const floa
     return CITLALI_DISPATCH_FLOAT(in_dtype, TZ, [&] {
         return CITLALI_DISPATCH_FLOAT(act_dtype, TO, [&] {
             launch_kernel(expert_gate_kernel<TZ, TO>, grid, 256, 0, stream, (const TZ*)gate_up, weights, (TO*)act, E, ff,
-                          run > 0 ? run : 1, kind, limit, alpha, tail_ff, tail_run > 0 ? tail_run : 1, tail_limit);
+                          run > 0 ? run : 1, kind, limit, alpha, tail_ff, tail_run > 0 ? tail_run : 1, tail_limit, bias, weight_input);
             return CITLALI_LAUNCH_CHECK();
         });
     });

@@ -29,6 +29,10 @@ int citlali_norm_inputs(const float* x, void* rows_out, float* sumsq, int rows, 
 
 // x[0..n) *= scale.
 int citlali_scale(float* x, size_t n, float scale, cudaStream_t stream);
+// x = cap tanh(x / cap) over n floats, cap > 0.
+int citlali_soft_cap(float* x, size_t n, float cap, cudaStream_t stream);
+// out[r] = [a[r] | b[r]] for two float32 matrices [rows, width], rounded once to out's type.
+int citlali_concat_rows(const float* a, const float* b, void* out, int out_dtype, int rows, int width, cudaStream_t stream);
 
 // out[r, :] = x[idx[r], :] * rsqrt(mean(x^2) + eps) * gain   (idx may be null: identity).
 int citlali_rms_norm(const float* x, const void* gain, int gain_dtype, const int32_t* row_index,
@@ -93,7 +97,7 @@ int citlali_attention_prefill(const void* q, int q_stride, const void* k_pool, c
                               const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_past,
                               void* out, int out_stride, int sequences, int max_new,
                               int nq, int nkv, int head_dim, int page_size, int window, int keep_first, float scale,
-                              cudaStream_t stream);
+                              float softcap, const float* gate, size_t gate_stride, cudaStream_t stream);
 
 // The same on tcgen05 (scores and output in tensor memory), for head size 128 and pages of 64.
 // total_rows: rows of q over all sequences; pool_pages: pages of the layer's key and value pools.
@@ -259,34 +263,40 @@ int citlali_gated_scan(const float* a, const float* coef, const float* side, int
 // [C, taps], no bias; kept inputs as in citlali_causal_conv; the caller stores them afterwards with citlali_conv_keep); q and
 // k heads then an RMS norm with q_gain / k_gain [d] (null: none) and the rotation of elements (2i, 2i+1), 2i < rot_dims, by
 // position * inv_freq[i].  q goes to q_out [rows, nq d]; with write_cache k and v go to the paged pools
-// [page, nkv, page_size, d] and [page, nkv, page_size, vd].
+// [page, nkv, page_size, d] and [page, nkv, page_size, vd].  bias (may be null): float32 [C], added to what the
+// convolution gives, ahead of the head norm.
 int citlali_conv_heads_prepare(const float* proj, int proj_stride, const float* taps_w, int taps, float* state,
                                size_t state_stride, size_t conv_off, const float* q_gain, const float* k_gain,
                                const float* inv_freq, int rot_dims, const int32_t* row_slot, const int32_t* row_pos,
                                const int32_t* page_table, int table_stride, void* k_pool, void* v_pool, int cache_dtype,
                                int page_size, void* q_out, int q_dtype, int rows, int nq, int nkv, int d, int vd, float eps,
-                               int write_cache, cudaStream_t stream);
+                               int write_cache, const float* bias, cudaStream_t stream);
 // out [rows, nq vd]: softmax attention of every row over the keys j <= pos of its slot with pos - j < window or
-// j < keep_first (window 0: all keys).  max_keys bounds the keys a row sees (shared memory).
+// j < keep_first (window 0: all keys).  max_keys bounds the keys a row sees (shared memory).  softcap > 0: the scaled
+// score s becomes softcap tanh(s / softcap).  gate (may be null): float32, out[r, c] *= sigmoid(gate[r gate_stride + c]).
 int citlali_attention_window(const void* q, int q_dtype, const void* k_pool, const void* v_pool, int cache_dtype,
                              const int32_t* page_table, int table_stride, const int32_t* row_slot, const int32_t* row_pos,
                              void* out, int rows, int nq, int nkv, int d, int vd, int page_size, int window, int keep_first,
-                             int max_keys, float scale, cudaStream_t stream);
+                             int max_keys, float scale, float softcap, const float* gate, size_t gate_stride,
+                             cudaStream_t stream);
 
 // ---- routed experts ----------------------------------------------------------------------------------------------------
 // weights [rows, E] = softmax(logits) at the `top` best experts among those of the `keep` best of `groups` equal groups of
 // neighbours (a group's score is its largest score; groups <= 1: no groups), 0 elsewhere; chosen [rows, top] (may be
 // null) their indices, best first.
-// The chosen experts' weights are multiplied by weight_scale.
+// The chosen experts' weights are multiplied by weight_scale.  score_kind 1: the scores are sigmoid(logits), each by itself.
 int citlali_moe_route(const float* logits, float* weights, int32_t* chosen, int rows, int E, int groups, int keep, int top,
-                      float weight_scale, cudaStream_t stream);
+                      float weight_scale, int score_kind, cudaStream_t stream);
 // act [rows, E ff + tail_ff] from gate_up [rows, 2 (E ff + tail_ff)], whose columns are, expert after expert, gate and up
 // alternating in runs of `run` (the last expert, which every row uses with weight 1, in runs of `tail_run`).  kind 0:
 // silu(g) u; kind 1: min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, -limit, limit) + 1).  Routed expert e's
 // activations are multiplied by weights[r, e]; where that is zero they are zeros and the inputs are not read.
+// kind 2: gelu_tanh(g) u.  bias (may be null): float32 [2 (E ff + tail_ff)] in the columns' order, added to gate and up
+// first.  weight_input != 0: the weight multiplies what the expert reads instead of what it gives, act(w g, w u): for
+// experts without biases that is the expert applied to w times its input.
 int citlali_expert_gate(const void* gate_up, int in_dtype, const float* weights, void* act, int act_dtype, int rows, int E,
                         int ff, int run, int kind, float limit, float alpha, int tail_ff, int tail_run, float tail_limit,
-                        cudaStream_t stream);
+                        const float* bias, int weight_input, cudaStream_t stream);
 // out = xielu(z + bias) over [rows, n]: u > 0: ap u^2 + u / 2; u <= 0: an (exp(u) - 1 - u) + u / 2.  bias may be null.
 int citlali_bias_xielu(const void* z, int z_dtype, const float* bias, float ap, float an, void* out, int out_dtype, int rows,
                        int n, cudaStream_t stream);
@@ -302,13 +312,16 @@ int citlali_moe_scale(void* act, int dtype, const float* weights, int rows, int 
 int citlali_latent_prepare(const float* proj, int proj_stride, int RQ, int R, int P, int has_kv, const float* q_weight,
                            const float* c_weight, const float* inv_freq, int rot_dims, const int32_t* row_slot,
                            const int32_t* row_pos, const int32_t* page_table, int table_stride, void* pool,
-                           int cache_dtype, int page_size, void* cq, int cq_dtype, int rows, float eps, cudaStream_t stream);
+                           int cache_dtype, int page_size, void* cq, int cq_dtype, int rows, float eps, int rot_halves,
+                           cudaStream_t stream);
 // y[r, h, n] = sum_k x[r * x_row + h * x_head + k] M[h * m_head + k * m_k + n * m_n]; with tail > 0 the elements
-// x[r, h, K .. K + tail) are rotated like a key part and copied to y[r, h, N ...]; with gate, y *= sigmoid(gate[r, h N + n]).
+// x[r, h, K .. K + tail) are rotated like a key part and copied to y[r, h, N ...]; with gate, y *= sigmoid(gate[r, h N + n])
+// (gate_per_head: sigmoid(gate[r, h])).  rot_halves (here and in citlali_latent_prepare): element i < rot_dims / 2 turns
+// with element i + rot_dims / 2 instead of 2i with 2i + 1.
 int citlali_heads_product(const void* x, int x_dtype, size_t x_row, int x_head, const void* M, int m_dtype, size_t m_head,
                           int m_k, int m_n, void* y, int y_dtype, size_t y_row, int y_head, int rows, int heads, int K,
                           int N, int tail, const float* inv_freq, int rot_dims, const int32_t* row_pos, const float* gate,
-                          size_t gate_stride, cudaStream_t stream);
+                          size_t gate_stride, int rot_halves, int gate_per_head, cudaStream_t stream);
 // out[r, h, :R] = sum_j p_j c_j over the keys lo..pos of the row's slot (lo = 0, or pos - window + 1 with a window),
 // p = softmax of scale * q[r, h, :] . pool[j, :], the denominator also counting exp(sink[h]) when sink is given.
 int citlali_latent_attention(const float* q, const void* pool, int cache_dtype, const int32_t* page_table,

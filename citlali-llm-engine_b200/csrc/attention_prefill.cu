@@ -14,6 +14,9 @@
 // p, query head j reads key/value head j / (heads / kv_heads).  The reference holds all scores
 // in memory and divides per term; this kernel's order differs from it by rounding only.
 //
+// Two options other designs use: a soft cap c on the scaled scores (s <- c tanh(s / c), float, ahead of the mask and the
+// softmax) and an output gate (the result's element is multiplied by the sigmoid of a float32 number of its own).
+//
 // The new tokens' keys and values are already in the cache when this runs, so prompts, and
 // runs of tokens that continue a sequence, are the same case: row r of sequence b sits at
 // position past[b] + r.
@@ -36,7 +39,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                          const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
                          const int32_t* __restrict__ seq_past,
                          __nv_bfloat16* __restrict__ out, int out_stride,
-                         int nq, int nkv, int window, int keep_first, float scale_log2) {
+                         int nq, int nkv, int window, int keep_first, float scale_log2, float cap_in, float cap_out,
+                         const float* __restrict__ gate, size_t gate_stride) {
     constexpr int kRowBytes = D * 2 + 16;
     constexpr int kTileBytes = kTileK * kRowBytes;
     constexpr int kChunksPerRow = D / 8;                     // 16-byte pieces of a row
@@ -134,6 +138,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 mma_16816(s[2 * np + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
             }
         }
+        if (cap_out > 0.0f) {
+            // s <- cap tanh(s scale / cap), then in units of log2: cap_in = 2 log2(e) scale / cap (so that ex2 gives
+            // exp(2 z)), cap_out = cap log2(e); scale_log2 is 1.  tanh z = 1 - 2 / (exp(2 z) + 1).
+#pragma unroll
+            for (int i = 0; i < kTileK / 8; ++i)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    s[i][c] = cap_out * (1.0f - __fdividef(2.0f, fast_exp2(s[i][c] * cap_in) + 1.0f));
+        }
         // mask, then the running maximum of each row (shared by the four lanes of a row)
         const int key_base = tile * kTileK + (lane & 3) * 2;
         float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -199,12 +212,20 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int col = (lane & 3) * 2;
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) {
-        if (r0 < n_new)
-            *reinterpret_cast<uint32_t*>(out + (size_t)(row0 + r0) * out_stride + (size_t)head * D + i * 8 + col) =
-                pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
-        if (r1 < n_new)
-            *reinterpret_cast<uint32_t*>(out + (size_t)(row0 + r1) * out_stride + (size_t)head * D + i * 8 + col) =
-                pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+        float a0 = o[i][0] * inv0, a1 = o[i][1] * inv0, b0 = o[i][2] * inv1, b1 = o[i][3] * inv1;
+        const size_t c = (size_t)head * D + i * 8 + col;
+        if (gate) {
+            if (r0 < n_new) {
+                const float2 g = *reinterpret_cast<const float2*>(gate + (size_t)(row0 + r0) * gate_stride + c);
+                a0 *= 1.0f / (1.0f + expf(-g.x)); a1 *= 1.0f / (1.0f + expf(-g.y));
+            }
+            if (r1 < n_new) {
+                const float2 g = *reinterpret_cast<const float2*>(gate + (size_t)(row0 + r1) * gate_stride + c);
+                b0 *= 1.0f / (1.0f + expf(-g.x)); b1 *= 1.0f / (1.0f + expf(-g.y));
+            }
+        }
+        if (r0 < n_new) *reinterpret_cast<uint32_t*>(out + (size_t)(row0 + r0) * out_stride + c) = pack_bf16(a0, a1);
+        if (r1 < n_new) *reinterpret_cast<uint32_t*>(out + (size_t)(row0 + r1) * out_stride + c) = pack_bf16(b0, b1);
     }
 }
 
@@ -212,7 +233,7 @@ template <int D>
 static int launch(const void* q, int q_stride, const void* k_pool, const void* v_pool, const int32_t* page_table,
                   int page_table_stride, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_past,
                   void* out, int out_stride, int sequences, int max_new, int nq, int nkv, int window, int keep_first,
-                  float scale, cudaStream_t stream) {
+                  float scale, float softcap, const float* gate, size_t gate_stride, cudaStream_t stream) {
     constexpr int smem = 5 * kTileK * (D * 2 + 16);
     auto kernel = attention_prefill_kernel<D>;
     static bool configured = false;
@@ -225,7 +246,10 @@ static int launch(const void* q, int q_stride, const void* k_pool, const void* v
     launch_kernel(kernel, grid, kWarps * 32, smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool,
                                                  (const __nv_bfloat16*)v_pool, page_table, page_table_stride, seq_start,
                                                  seq_slot, seq_past, (__nv_bfloat16*)out, out_stride, nq, nkv, window,
-                                                 window > 0 ? keep_first : 0, scale * 1.4426950408889634f);
+                                                 window > 0 ? keep_first : 0,
+                                                 softcap > 0.0f ? 1.0f : scale * 1.4426950408889634f,
+                                                 softcap > 0.0f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.0f,
+                                                 softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f, gate, gate_stride);
     return CITLALI_LAUNCH_CHECK();
 }
 
@@ -253,7 +277,8 @@ extern "C" int citlali_attention_prefill(const void* q, int q_stride, const void
                                          const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_past,
                                          void* out, int out_stride, int sequences, int max_new,
                                          int nq, int nkv, int head_dim, int page_size, int window, int keep_first,
-                                         float scale, cudaStream_t stream) {
+                                         float scale, float softcap, const float* gate, size_t gate_stride,
+                                         cudaStream_t stream) {
     if (sequences <= 0 || max_new <= 0) return 0;
     if (!citlali_attention_prefill_supports(head_dim, page_size)) {
         set_last_error("attention_prefill: no kernel for head size %d with pages of %d (head sizes 16..128 in steps of 16 "
@@ -264,12 +289,16 @@ extern "C" int citlali_attention_prefill(const void* q, int q_stride, const void
         set_last_error("attention_prefill: bad head counts (%d over %d) or too many sequences (%d)", nq, nkv, sequences);
         return kBadShape;
     }
+    if (gate != nullptr && (gate_stride % 2 != 0 || ((uintptr_t)gate & 7u))) {
+        set_last_error("attention_prefill: the gate's rows must be 8-byte aligned (row pitch %zu floats)", gate_stride);
+        return kBadAlignment;
+    }
     if (q_stride % 8 != 0 || out_stride % 2 != 0 || ((uintptr_t)q & 15u) || ((uintptr_t)out & 3u)) {
         set_last_error("attention_prefill: query rows must be 16-byte aligned (row pitch %d elements)", q_stride);
         return kBadAlignment;
     }
 #define CITLALI_FA(DD) case DD: return fa::launch<DD>(q, q_stride, k_pool, v_pool, page_table, page_table_stride, seq_start, \
-                                                      seq_slot, seq_past, out, out_stride, sequences, max_new, nq, nkv, window, keep_first, scale, stream)
+                                                      seq_slot, seq_past, out, out_stride, sequences, max_new, nq, nkv, window, keep_first, scale, softcap, gate, gate_stride, stream)
     switch (head_dim) {
         CITLALI_FA(16); CITLALI_FA(32); CITLALI_FA(48); CITLALI_FA(64); CITLALI_FA(80); CITLALI_FA(96); CITLALI_FA(112);
         CITLALI_FA(128); CITLALI_FA(256);

@@ -65,6 +65,28 @@ __global__ void scale_kernel(float* __restrict__ x, size_t n, float scale) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] *= scale;
 }
 
+// x = cap tanh(x / cap) over n floats (a soft cap on the logits), in 32-bit.
+__global__ void soft_cap_kernel(float* __restrict__ x, size_t n, float cap, float inv_cap) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+// out[r] = [a[r] | b[r]] (two float32 matrices of `width` columns side by side), rounded once to out's type.
+template <typename TO>
+__global__ void concat_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, TO* __restrict__ out, size_t rows,
+                                   int width) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    const size_t n = rows * 2 * (size_t)width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / (2 * (size_t)width);
+        const int c = (int)(i % (2 * (size_t)width));
+        stf(out, i, c < width ? a[r * width + c] : b[r * width + c - width]);
+    }
+}
+
 // inv = rsqrt(sum x^2 / n + eps); y = x * inv * gain (reference: rms_norm_kernel,
 // kernels.cu:73-92, which runs one block per vector; here one block per row).
 template <typename TG, typename TO>
@@ -200,6 +222,27 @@ extern "C" int citlali_scale(float* x, size_t n, float scale, cudaStream_t strea
     const size_t blocks = (n + 255) / 256;
     launch_kernel(scale_kernel, (int)(blocks < 4096 ? blocks : 4096), 256, 0, stream, x, n, scale);
     return CITLALI_LAUNCH_CHECK();
+}
+
+extern "C" int citlali_soft_cap(float* x, size_t n, float cap, cudaStream_t stream) {
+    if (n == 0) return 0;
+    if (!(cap > 0.0f)) {
+        set_last_error("soft_cap: the cap %g must be positive", (double)cap);
+        return kBadShape;
+    }
+    const size_t blocks = (n + 255) / 256;
+    launch_kernel(soft_cap_kernel, (int)(blocks < 4096 ? blocks : 4096), 256, 0, stream, x, n, cap, 1.0f / cap);
+    return CITLALI_LAUNCH_CHECK();
+}
+
+extern "C" int citlali_concat_rows(const float* a, const float* b, void* out, int out_dtype, int rows, int width,
+                                   cudaStream_t stream) {
+    if (rows <= 0 || width <= 0) return 0;
+    const size_t n = (size_t)rows * 2 * width, blocks = (n + 255) / 256;
+    return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
+        launch_kernel(concat_rows_kernel<TO>, (int)(blocks < 8192 ? blocks : 8192), 256, 0, stream, a, b, (TO*)out, (size_t)rows, width);
+        return CITLALI_LAUNCH_CHECK();
+    });
 }
 
 extern "C" int citlali_rms_norm(const float* x, const void* gain, int gain_dtype, const int32_t* row_index,

@@ -6,10 +6,12 @@
 // the walk itself reads R + P numbers a token whatever the number of heads.
 //
 //   latent_prepare     one block a row: RMS norm of the query latent and of c (plain weights), rotation of r by the
-//                      row's position (pairs (2i, 2i+1), angle = float(position) * inv_freq[i]), cache write.
+//                      row's position (angle = float(position) * inv_freq[i]; element pairs (2i, 2i+1), or with
+//                      rot_halves (i, i + rot_dims / 2)), cache write.
 //   heads_product      y[row, h, :] = x[row, h, :] . M_h for a matrix per head given by strides (W_uk as stored, or
 //                      W_uv transposed); optional extras: a tail of the row rotated and copied behind the product
-//                      (the query's rotated part), or a sigmoid gate on the result.  bfloat16 matrices run on the
+//                      (the query's rotated part), or a sigmoid gate on the result (a number an element, or with
+//                      gate_per_head a number a head).  bfloat16 matrices run on the
 //                      tensor cores (heads_product_mma), float32 ones on CUDA cores.
 //   latent_attention   one warp a (row, head): keys lo..pos in ascending order, lo = 0 or pos - window + 1, online
 //                      softmax in float32 whose denominator also counts exp(sink) once.
@@ -19,6 +21,22 @@
 
 namespace citlali {
 
+// Element i of a vector of n whose first rot_dims elements turn by the position: the pair of i is i ^ 1 (neighbours) or,
+// with halves, i +- rot_dims / 2; the pair's first element u becomes u cos - v sin, its second v cos + u sin.
+template <typename TX>
+__device__ __forceinline__ float rotated_element(const TX* __restrict__ src, int i, int rot_dims, int halves, int pos,
+                                                 const float* __restrict__ inv_freq) {
+    const float self = ldf(src, i);
+    if (i >= rot_dims) return self;
+    const int half = rot_dims >> 1;
+    const bool first = halves ? i < half : !(i & 1);
+    const int f = halves ? (first ? i : i - half) : i >> 1;
+    const float other = ldf(src, halves ? (first ? i + half : i - half) : i ^ 1);
+    float sn, cs;
+    sincosf((float)pos * inv_freq[f], &sn, &cs);
+    return first ? self * cs - other * sn : self * cs + other * sn;
+}
+
 // proj [rows, proj_stride] float32: query latent (RQ) | c (R) | r (P) | ...   (has_kv = 0: no c and r in the row).
 template <typename TC, typename TQ>
 __global__ void __launch_bounds__(256)
@@ -26,7 +44,7 @@ latent_prepare_kernel(const float* __restrict__ proj, int proj_stride, int RQ, i
                       const float* __restrict__ q_weight, const float* __restrict__ c_weight,
                       const float* __restrict__ inv_freq, int rot_dims, const int32_t* __restrict__ row_slot,
                       const int32_t* __restrict__ row_pos, const int32_t* __restrict__ page_table, int table_stride,
-                      TC* __restrict__ pool, int page_size, TQ* __restrict__ cq, float eps) {
+                      TC* __restrict__ pool, int page_size, TQ* __restrict__ cq, float eps, int rot_halves) {
     __shared__ float scratch[32];
     dependents_may_launch();
     wait_for_predecessor();
@@ -48,6 +66,10 @@ latent_prepare_kernel(const float* __restrict__ proj, int proj_stride, int RQ, i
     TC* dst = pool + ((size_t)page * page_size + pos % page_size) * (R + P);
     for (int i = threadIdx.x; i < R; i += blockDim.x) stf(dst, i, c[i] * inv * c_weight[i]);
     const float* r = c + R;
+    if (rot_halves) {
+        for (int i = threadIdx.x; i < P; i += blockDim.x) stf(dst, R + i, rotated_element(r, i, rot_dims, 1, pos, inv_freq));
+        return;
+    }
     for (int i = threadIdx.x; i < P / 2; i += blockDim.x) {
         float a = r[2 * i], b = r[2 * i + 1];
         if (2 * i + 1 < rot_dims) {
@@ -68,7 +90,17 @@ template <typename TX, typename TY>
 __device__ __forceinline__ void rotate_tail(const TX* __restrict__ x, size_t x_row, int x_head, TY* __restrict__ y, size_t y_row,
                                             int y_head, int h, int row0, int count, int rows, int K, int N, int tail,
                                             const float* __restrict__ inv_freq, int rot_dims,
-                                            const int32_t* __restrict__ row_pos) {
+                                            const int32_t* __restrict__ row_pos, int rot_halves) {
+    if (rot_halves) {
+        for (int e = threadIdx.x; e < count * tail; e += blockDim.x) {
+            const int r = e / tail, i = e % tail, row = row0 + r;
+            if (row >= rows) continue;
+            const TX* src = x + (size_t)row * x_row + (size_t)h * x_head + K;
+            stf(y + (size_t)row * y_row + (size_t)h * y_head + N, i,
+                rotated_element(src, i, rot_dims, 1, rot_dims > 0 ? row_pos[row] : 0, inv_freq));
+        }
+        return;
+    }
     const int pairs = (tail + 1) / 2;
     for (int e = threadIdx.x; e < count * pairs; e += blockDim.x) {
         const int r = e / pairs, i = e % pairs, row = row0 + r;
@@ -98,7 +130,7 @@ __global__ void __launch_bounds__(256)
 heads_product_kernel(const TX* __restrict__ x, size_t x_row, int x_head, const TM* __restrict__ M, size_t m_head, int m_k,
                      int m_n, TY* __restrict__ y, size_t y_row, int y_head, int rows, int K, int N, int tail,
                      const float* __restrict__ inv_freq, int rot_dims, const int32_t* __restrict__ row_pos,
-                     const float* __restrict__ gate, size_t gate_stride) {
+                     const float* __restrict__ gate, size_t gate_stride, int rot_halves, int gate_per_head) {
     __shared__ float xs[8][33];
     __shared__ float ms[32][65];
     dependents_may_launch();
@@ -132,12 +164,12 @@ heads_product_kernel(const TX* __restrict__ x, size_t x_row, int x_head, const T
             const int row = row0 + tr + 4 * half;
             if (row >= rows) continue;
             float v = half ? acc1 : acc0;
-            if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)row * gate_stride + (size_t)h * N + n]));
+            if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)row * gate_stride + (gate_per_head ? (size_t)h : (size_t)h * N + n)]));
             stf(y, (size_t)row * y_row + (size_t)h * y_head + n, v);
         }
     }
     if (tail > 0 && blockIdx.z == 0)
-        rotate_tail(x, x_row, x_head, y, y_row, y_head, h, row0, 8, rows, K, N, tail, inv_freq, rot_dims, row_pos);
+        rotate_tail(x, x_row, x_head, y, y_row, y_head, h, row0, 8, rows, K, N, tail, inv_freq, rot_dims, row_pos, rot_halves);
 }
 
 // The same product on the tensor cores for bfloat16 matrices: a block of four warps computes 64 rows x 64 columns of one
@@ -149,7 +181,8 @@ __global__ void __launch_bounds__(128)
 heads_product_mma_kernel(const TX* __restrict__ x, size_t x_row, int x_head, const __nv_bfloat16* __restrict__ M,
                          size_t m_head, int m_k, int m_n, TY* __restrict__ y, size_t y_row, int y_head, int rows, int K,
                          int N, int tail, const float* __restrict__ inv_freq, int rot_dims,
-                         const int32_t* __restrict__ row_pos, const float* __restrict__ gate, size_t gate_stride) {
+                         const int32_t* __restrict__ row_pos, const float* __restrict__ gate, size_t gate_stride,
+                         int rot_halves, int gate_per_head) {
     constexpr int KT = 64, LD = KT + 8;
     __shared__ __align__(16) __nv_bfloat16 xs[64][LD];
     __shared__ __align__(16) __nv_bfloat16 ms[64][LD];
@@ -230,11 +263,11 @@ heads_product_mma_kernel(const TX* __restrict__ x, size_t x_row, int x_head, con
             const int row = row0 + warp * 16 + g + (c >> 1) * 8, col = n0 + n * 8 + t * 2 + (c & 1);
             if (row >= rows || col >= N) continue;
             float v = acc[n][c];
-            if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)row * gate_stride + (size_t)h * N + col]));
+            if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)row * gate_stride + (gate_per_head ? (size_t)h : (size_t)h * N + col)]));
             stf(y, (size_t)row * y_row + (size_t)h * y_head + col, v);
         }
     if (tail > 0 && blockIdx.z == 0)
-        rotate_tail(x, x_row, x_head, y, y_row, y_head, h, row0, 64, rows, K, N, tail, inv_freq, rot_dims, row_pos);
+        rotate_tail(x, x_row, x_head, y, y_row, y_head, h, row0, 64, rows, K, N, tail, inv_freq, rot_dims, row_pos, rot_halves);
 }
 
 // q [rows, H, E] float32 (E = R + P: the query in the latent's coordinates, then its rotated part); the cache's pool
@@ -303,7 +336,7 @@ extern "C" int citlali_latent_prepare(const float* proj, int proj_stride, int RQ
                                       const float* q_weight, const float* c_weight, const float* inv_freq, int rot_dims,
                                       const int32_t* row_slot, const int32_t* row_pos, const int32_t* page_table,
                                       int table_stride, void* pool, int cache_dtype, int page_size, void* cq, int cq_dtype,
-                                      int rows, float eps, cudaStream_t stream) {
+                                      int rows, float eps, int rot_halves, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (rot_dims < 0 || rot_dims > P || (rot_dims & 1)) {
         set_last_error("latent_prepare: %d rotated dimensions of a key part of %d", rot_dims, P);
@@ -313,7 +346,7 @@ extern "C" int citlali_latent_prepare(const float* proj, int proj_stride, int RQ
         return CITLALI_DISPATCH_FLOAT(cq_dtype, TQ, [&] {
             launch_kernel(latent_prepare_kernel<TC, TQ>, rows, 256, 0, stream, proj, proj_stride, RQ, R, P, has_kv, q_weight,
                           c_weight, inv_freq, rot_dims, row_slot, row_pos, page_table, table_stride, (TC*)pool, page_size,
-                          (TQ*)cq, eps);
+                          (TQ*)cq, eps, rot_halves);
             return CITLALI_LAUNCH_CHECK();
         });
     });
@@ -322,7 +355,8 @@ extern "C" int citlali_latent_prepare(const float* proj, int proj_stride, int RQ
 extern "C" int citlali_heads_product(const void* x, int x_dtype, size_t x_row, int x_head, const void* M, int m_dtype,
                                      size_t m_head, int m_k, int m_n, void* y, int y_dtype, size_t y_row, int y_head,
                                      int rows, int heads, int K, int N, int tail, const float* inv_freq, int rot_dims,
-                                     const int32_t* row_pos, const float* gate, size_t gate_stride, cudaStream_t stream) {
+                                     const int32_t* row_pos, const float* gate, size_t gate_stride, int rot_halves,
+                                     int gate_per_head, cudaStream_t stream) {
     if (rows <= 0 || heads <= 0) return 0;
     if (heads > 65535 || (N + 63) / 64 > 65535) {
         set_last_error("heads_product: %d heads or %d columns exceed the grid", heads, N);
@@ -338,7 +372,7 @@ extern "C" int citlali_heads_product(const void* x, int x_dtype, size_t x_row, i
             return CITLALI_DISPATCH_FLOAT(y_dtype, TY, [&] {
                 launch_kernel(heads_product_mma_kernel<TX, TY>, grid, 128, 0, stream, (const TX*)x, x_row, x_head,
                               (const __nv_bfloat16*)M, m_head, m_k, m_n, (TY*)y, y_row, y_head, rows, K, N, tail, inv_freq,
-                              rot_dims, row_pos, gate, gate_stride);
+                              rot_dims, row_pos, gate, gate_stride, rot_halves, gate_per_head);
                 return CITLALI_LAUNCH_CHECK();
             });
         });
@@ -349,7 +383,7 @@ extern "C" int citlali_heads_product(const void* x, int x_dtype, size_t x_row, i
             return CITLALI_DISPATCH_FLOAT(y_dtype, TY, [&] {
                 launch_kernel(heads_product_kernel<TX, TM, TY>, grid, 256, 0, stream, (const TX*)x, x_row, x_head, (const TM*)M,
                               m_head, m_k, m_n, (TY*)y, y_row, y_head, rows, K, N, tail, inv_freq, rot_dims, row_pos, gate,
-                              gate_stride);
+                              gate_stride, rot_halves, gate_per_head);
                 return CITLALI_LAUNCH_CHECK();
             });
         });

@@ -1,6 +1,7 @@
 // Routed experts: which experts a token uses and with what weight.
 //
-//   moe_route       one warp a row.  scores = softmax(logits) over all E experts (float32).  The experts form `groups`
+//   moe_route       one warp a row.  scores = softmax(logits) over all E experts (float32), or with score_kind 1 the sigmoid of
+//                   every logit by itself.  The experts form `groups`
 //                   equal groups of neighbours; a group's score is its largest score, and only experts of the `keep` best
 //                   groups can be chosen (groups <= 1 or keep >= groups: all can).  The `top` largest scores among those are
 //                   chosen (of equal scores the lower index first); their weights are the scores themselves, not
@@ -17,7 +18,7 @@ constexpr int kMaxExpertsPerLane = 16;      // E <= 512
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, float* __restrict__ weights, int32_t* __restrict__ chosen, int rows, int E,
-                 int groups, int keep, int top, float weight_scale) {
+                 int groups, int keep, int top, float weight_scale, int score_kind) {
     dependents_may_launch();
     wait_for_predecessor();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -31,17 +32,22 @@ moe_route_kernel(const float* __restrict__ logits, float* __restrict__ weights, 
         s[j] = e < E ? z[e] : -INFINITY;
         m = fmaxf(m, s[j]);
     }
-    m = warp_max(m);
-    float sum = 0.0f;
+    if (score_kind == 1) {
 #pragma unroll
-    for (int j = 0; j < kMaxExpertsPerLane; ++j) {
-        const int e = lane + 32 * j;
-        s[j] = e < E ? expf(s[j] - m) : 0.0f;
-        sum += s[j];
+        for (int j = 0; j < kMaxExpertsPerLane; ++j) s[j] = lane + 32 * j < E ? 1.0f / (1.0f + expf(-s[j])) : 0.0f;
+    } else {
+        m = warp_max(m);
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kMaxExpertsPerLane; ++j) {
+            const int e = lane + 32 * j;
+            s[j] = e < E ? expf(s[j] - m) : 0.0f;
+            sum += s[j];
+        }
+        sum = warp_sum(sum);
+#pragma unroll
+        for (int j = 0; j < kMaxExpertsPerLane; ++j) s[j] = s[j] / sum;
     }
-    sum = warp_sum(sum);
-#pragma unroll
-    for (int j = 0; j < kMaxExpertsPerLane; ++j) s[j] = s[j] / sum;
     // which experts may be chosen: bit j of `open` for expert lane + 32 j
     unsigned open = 0;
 #pragma unroll
@@ -163,8 +169,12 @@ __global__ void moe_scale_vec_kernel(__nv_bfloat16* __restrict__ act, const floa
 using namespace citlali;
 
 extern "C" int citlali_moe_route(const float* logits, float* weights, int32_t* chosen, int rows, int E, int groups, int keep,
-                                 int top, float weight_scale, cudaStream_t stream) {
+                                 int top, float weight_scale, int score_kind, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (score_kind != 0 && score_kind != 1) {
+        set_last_error("moe_route: score kind %d is neither softmax (0) nor sigmoid (1)", score_kind);
+        return kBadShape;
+    }
     if (E <= 0 || E > 32 * kMaxExpertsPerLane || top <= 0 || top > E) {
         set_last_error("moe_route: %d experts (at most %d), %d chosen", E, 32 * kMaxExpertsPerLane, top);
         return kBadShape;
@@ -173,7 +183,8 @@ extern "C" int citlali_moe_route(const float* logits, float* weights, int32_t* c
         set_last_error("moe_route: %d experts in %d groups of which %d are kept cannot give %d experts", E, groups, keep, top);
         return kBadShape;
     }
-    launch_kernel(moe_route_kernel, (rows + 3) / 4, 128, 0, stream, logits, weights, chosen, rows, E, groups, keep, top, weight_scale);
+    launch_kernel(moe_route_kernel, (rows + 3) / 4, 128, 0, stream, logits, weights, chosen, rows, E, groups, keep, top, weight_scale,
+                  score_kind);
     return CITLALI_LAUNCH_CHECK();
 }
 

@@ -5,9 +5,12 @@
 //                        step's rows or from the sequence's kept inputs), for q and k heads an RMS norm with a weight
 //                        shared by the heads and the rotation of the first rot_dims elements in neighbouring pairs
 //                        (2i, 2i+1) by position * inv_freq[i]; q goes to a buffer, k and v to the row's place in the
-//                        paged cache.  All float32 until the one rounding at the store.
+//                        paged cache.  All float32 until the one rounding at the store.  An optional bias a channel is
+//                        added to what the convolution gives (with one tap: to the projection itself).
 //   attention_window     one block a (row, query head): keys j <= pos with pos - j < window or j < keep_first (window 0:
-//                        every key); scores, softmax and the weighted sum in float32.  The keys are dealt to 32 groups of
+//                        every key); scores, softmax and the weighted sum in float32; with a soft cap c the scaled score s
+//                        becomes c tanh(s / c) before the softmax; with a gate the head's output element i is multiplied
+//                        by sigmoid(gate[row, head vd + i]).  The keys are dealt to 32 groups of
 //                        eight lanes by their place among the visible keys, each group keeps a running softmax of its own,
 //                        and the groups are merged in one fixed order: a row's result does not depend on the step it came
 //                        in, and no score is ever stored, so the number of keys has no limit.
@@ -26,7 +29,8 @@ conv_heads_prepare_kernel(const float* __restrict__ proj, int proj_stride, const
                           const float* __restrict__ q_gain, const float* __restrict__ k_gain, const float* __restrict__ inv_freq,
                           int rot_dims, const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
                           const int32_t* __restrict__ page_table, int table_stride, T* __restrict__ k_pool, T* __restrict__ v_pool,
-                          int page_size, TQ* __restrict__ q_out, int nq, int nkv, int d, int vd, float eps, int write_cache) {
+                          int page_size, TQ* __restrict__ q_out, int nq, int nkv, int d, int vd, float eps, int write_cache,
+                          const float* __restrict__ bias) {
     dependents_may_launch();
     wait_for_predecessor();
     const int row = blockIdx.x, lane = threadIdx.x & 31;
@@ -56,6 +60,7 @@ conv_heads_prepare_kernel(const float* __restrict__ proj, int proj_stride, const
                 else u = kept[(size_t)(taps - 1 - back + in_step) * C + c];
                 acc = fmaf(taps_w[(size_t)c * taps + (taps - 1 - back)], u, acc);
             }
+            if (bias) acc += bias[c];
         }
         x[j] = acc;
         ss = fmaf(acc, acc, ss);
@@ -137,7 +142,8 @@ __global__ void __launch_bounds__(kWinWarps * 32, PL <= 16 ? 2 : 1)
 attention_window_kernel(const TQ* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                         const int32_t* __restrict__ page_table, int table_stride, const int32_t* __restrict__ row_slot,
                         const int32_t* __restrict__ row_pos, TQ* __restrict__ out, int nq, int nkv, int d, int vd,
-                        int page_size, int window, int keep_first, float scale) {
+                        int page_size, int window, int keep_first, float scale, float softcap, const float* __restrict__ gate,
+                        size_t gate_stride) {
     extern __shared__ float smem[];                            // [32 groups][vd] weighted sums, then [32] maxima, [32] sums
     dependents_may_launch();
     wait_for_predecessor();
@@ -158,7 +164,9 @@ attention_window_kernel(const TQ* __restrict__ q, const T* __restrict__ k_pool, 
         acc[c] = 0.0f;
     }
     float m = -INFINITY, l = 0.0f;
+    const float inv_cap = softcap > 0.0f ? 1.0f / softcap : 0.0f;
     auto take = [&](float s, const float (&v)[PL]) {           // one key's score and value into the group's running softmax
+        if (softcap > 0.0f) s = softcap * tanhf(s * inv_cap);
         if (s > m) {                                           // the maximum grows: what the group has is scaled down
             const float f = expf(m - s);                       // (zero the first time)
             l *= f;
@@ -257,19 +265,22 @@ attention_window_kernel(const TQ* __restrict__ q, const T* __restrict__ k_pool, 
             z = fmaf(f, gl[j], z);
             a = fmaf(f, sums[j * vd + i], a);
         }
-        stf(out, (size_t)row * nq * vd + (size_t)head * vd + i, a / z);
+        float r = a / z;
+        if (gate) r *= 1.0f / (1.0f + expf(-gate[(size_t)row * gate_stride + (size_t)head * vd + i]));
+        stf(out, (size_t)row * nq * vd + (size_t)head * vd + i, r);
     }
 }
 
 template <typename T, typename TQ, int PL, bool VEC>
 static int launch_window(const void* q, const void* k_pool, const void* v_pool, const int32_t* page_table, int table_stride,
                          const int32_t* row_slot, const int32_t* row_pos, void* out, int rows, int nq, int nkv, int d, int vd,
-                         int page_size, int window, int keep_first, float scale, cudaStream_t stream) {
+                         int page_size, int window, int keep_first, float scale, float softcap, const float* gate,
+                         size_t gate_stride, cudaStream_t stream) {
     const size_t smem = (size_t)(32 * vd + 64) * sizeof(float);
     dim3 grid(rows, nq);
     launch_kernel(attention_window_kernel<T, TQ, PL, VEC>, grid, kWinWarps * 32, smem, stream, (const TQ*)q, (const T*)k_pool,
                   (const T*)v_pool, page_table, table_stride, row_slot, row_pos, (TQ*)out, nq, nkv, d, vd, page_size, window,
-                  keep_first, scale);
+                  keep_first, scale, softcap, gate, gate_stride);
     return CITLALI_LAUNCH_CHECK();
 }
 
@@ -282,7 +293,8 @@ extern "C" int citlali_conv_heads_prepare(const float* proj, int proj_stride, co
                                           const float* inv_freq, int rot_dims, const int32_t* row_slot, const int32_t* row_pos,
                                           const int32_t* page_table, int table_stride, void* k_pool, void* v_pool,
                                           int cache_dtype, int page_size, void* q_out, int q_dtype, int rows, int nq, int nkv,
-                                          int d, int vd, float eps, int write_cache, cudaStream_t stream) {
+                                          int d, int vd, float eps, int write_cache, const float* bias,
+                                          cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (nq <= 0 || nkv <= 0 || d <= 0 || vd <= 0 || d > 32 * kMaxPerLane || vd > 32 * kMaxPerLane || taps < 1 || page_size <= 0) {
         set_last_error("conv_heads_prepare: %d and %d heads of %d (values %d, at most %d), %d taps", nq, nkv, d, vd,
@@ -301,7 +313,7 @@ extern "C" int citlali_conv_heads_prepare(const float* proj, int proj_stride, co
             launch_kernel(conv_heads_prepare_kernel<T, TQ>, grid, kHeadWarps * 32, 0, stream, proj, proj_stride, taps_w, taps,
                           (const float*)state, state_stride, conv_off, q_gain, k_gain, inv_freq, rot_dims, row_slot, row_pos,
                           page_table, table_stride, (T*)k_pool, (T*)v_pool, page_size, (TQ*)q_out, nq, nkv, d, vd, eps,
-                          write_cache);
+                          write_cache, bias);
             return CITLALI_LAUNCH_CHECK();
         });
     });
@@ -311,7 +323,7 @@ extern "C" int citlali_attention_window(const void* q, int q_dtype, const void* 
                                         const int32_t* page_table, int table_stride, const int32_t* row_slot,
                                         const int32_t* row_pos, void* out, int rows, int nq, int nkv, int d, int vd,
                                         int page_size, int window, int keep_first, int max_keys, float scale,
-                                        cudaStream_t stream) {
+                                        float softcap, const float* gate, size_t gate_stride, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || vd <= 0 || nq > 65535 || window < 0 || keep_first < 0) {
         set_last_error("attention_window: %d query heads over %d key/value heads of %d (values %d), window %d, %d kept", nq, nkv,
@@ -330,14 +342,14 @@ extern "C" int citlali_attention_window(const void* q, int q_dtype, const void* 
     do {                                                                                                                  \
         if (vec) {                                                                                                        \
             if constexpr (sizeof(T) == 2) {                                                                               \
-                if (big <= 64) return launch_window<T, TQ, 8, true>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, stream); \
-                if (big <= 128) return launch_window<T, TQ, 16, true>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, stream); \
-                return launch_window<T, TQ, 32, true>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, stream); \
+                if (big <= 64) return launch_window<T, TQ, 8, true>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, softcap, gate, gate_stride, stream); \
+                if (big <= 128) return launch_window<T, TQ, 16, true>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, softcap, gate, gate_stride, stream); \
+                return launch_window<T, TQ, 32, true>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, softcap, gate, gate_stride, stream); \
             }                                                                                                             \
         }                                                                                                                 \
-        if (big <= 64) return launch_window<T, TQ, 8, false>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, stream); \
-        if (big <= 128) return launch_window<T, TQ, 16, false>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, stream); \
-        return launch_window<T, TQ, 32, false>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, stream); \
+        if (big <= 64) return launch_window<T, TQ, 8, false>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, softcap, gate, gate_stride, stream); \
+        if (big <= 128) return launch_window<T, TQ, 16, false>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, softcap, gate, gate_stride, stream); \
+        return launch_window<T, TQ, 32, false>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, softcap, gate, gate_stride, stream); \
     } while (0)
     return CITLALI_DISPATCH_FLOAT(cache_dtype, T, [&] {
         return CITLALI_DISPATCH_FLOAT(q_dtype, TQ, [&]() -> int { CITLALI_WINDOW(T, TQ); });

@@ -34,6 +34,8 @@ def _build_layers(spec: ModelSpec):
 def expected_tensors(spec: ModelSpec) -> List[TensorSpec]:
     """Every checkpoint tensor the model reads, in a fixed order.  No device is touched."""
     specs = [TensorSpec(spec.embedding_name, (spec.vocab_size, spec.hidden_size), "matrix")]
+    if spec.embedding_norm is not None:
+        specs.extend(build_part("norm", spec.embedding_norm).tensor_specs())
     for block in _build_layers(spec):
         specs.extend(block.tensor_specs())
     specs.extend(build_part("norm", spec.final_norm).tensor_specs())
@@ -61,6 +63,15 @@ class DecoderModel:
         self.ctx = ctx
         self.layers = _build_layers(spec)
         self.final_norm = build_part("norm", spec.final_norm)
+        self.embedding_norm = build_part("norm", spec.embedding_norm) if spec.embedding_norm is not None else None
+        self.keeps_embedding_output = any(getattr(block, "needs_embedding_output", False) for block in self.layers)
+        require(spec.residual_streams is None or (self.embedding_norm is None and not self.keeps_embedding_output),
+                "a norm on the embedding's rows and blocks that read them again work on one residual stream")
+        seen: Dict[int, int] = {}
+        self.visits = []                       # per schedule step: how often its layer has run before it
+        for step in spec.schedule:
+            self.visits.append(seen.get(step.layer, 0))
+            seen[step.layer] = self.visits[-1] + 1
         self.head = DenseLinear([spec.head_name], [spec.vocab_size], spec.hidden_size)
         self.embedding: Optional[torch.Tensor] = None
         self.tied = None
@@ -87,6 +98,8 @@ class DecoderModel:
         for block in self.layers:
             block.bind(weights, ctx)
         self.final_norm.bind(weights, ctx)
+        if self.embedding_norm is not None:
+            self.embedding_norm.bind(weights, ctx)
         tie = spec.tie_head_to_embedding
         if tie is None:
             tie = spec.head_name not in weights      # absent head: reuse the embedding (qwen_model.cpp:71-75)
@@ -115,6 +128,10 @@ class DecoderModel:
         if streams is None:
             x = torch.empty((batch.rows, spec.hidden_size), dtype=torch.float32, device=ctx.device)
             ops.embed_rows(self.embedding, batch.tokens, x, ctx.error_flag, emb_scale)
+            if self.embedding_norm is not None:
+                x = self.embedding_norm.forward(x, out_dtype=torch.float32)
+            # blocks that read the embedding's rows again get them apart from the residual, which the layers change in place
+            batch.embedding_output = x.clone() if self.keeps_embedding_output else None
         else:                       # every stream starts as the embedding's rows
             x = torch.empty((streams, batch.rows, spec.hidden_size), dtype=torch.float32, device=ctx.device)
             ops.embed_rows_streams(self.embedding, batch.tokens, x, ctx.error_flag, emb_scale)
@@ -131,6 +148,7 @@ class DecoderModel:
             batch.rows_carry_in, batch.rows_carry = batch.rows_carry, None
             batch.normed_carry_in, batch.normed_carry = batch.normed_carry, None
             batch.next_first_norm = first_norms[spec.schedule[i + 1].layer] if i + 1 < len(spec.schedule) else None
+            batch.visit = self.visits[i]
             if batch.stream_write is not None and not getattr(self.layers[step.layer], "takes_stream_write", False):
                 ops.hyper_write(x, *batch.stream_write)      # the block ahead left a write-back that this one would not do
                 batch.stream_write = None
@@ -138,6 +156,7 @@ class DecoderModel:
         batch.norm_carry_in = batch.norm_carry = None
         batch.rows_carry_in = batch.rows_carry = None
         batch.normed_carry_in = batch.normed_carry = batch.next_first_norm = None
+        batch.embedding_output = None
         if batch.stream_write is not None:              # the last layer's last write-back into the streams
             ops.hyper_write(x, *batch.stream_write)
             batch.stream_write = None
@@ -153,4 +172,6 @@ class DecoderModel:
         logits = self.head.forward(h, out_dtype=torch.float32)
         if spec.logit_scale is not None:
             ops.scale_(logits, float(spec.logit_scale))
+        if spec.logit_softcap is not None:
+            ops.soft_cap_(logits, float(spec.logit_softcap))
         return logits

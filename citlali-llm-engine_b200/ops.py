@@ -114,6 +114,23 @@ def scale_(x: torch.Tensor, scale: float):
     _check(lib().citlali_scale(_ptr(x), ctypes.c_size_t(x.numel()), _f(scale), _stream()), "scale")
 
 
+def soft_cap_(x: torch.Tensor, cap: float):
+    """x = cap tanh(x / cap) in place (float32)."""
+    _need_cuda(x)
+    require(x.dtype == torch.float32 and cap > 0.0, "soft_cap_: float32 only, with a positive cap")
+    _check(lib().citlali_soft_cap(_ptr(x), ctypes.c_size_t(x.numel()), _f(cap), _stream()), "soft_cap")
+
+
+def concat_rows(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor):
+    """``out[r] = [a[r] | b[r]]`` for two float32 matrices of one shape, rounded once to ``out``'s dtype."""
+    _need_cuda(a, b, out)
+    rows, width = a.shape
+    require(a.dtype == torch.float32 and b.dtype == torch.float32 and b.shape == a.shape and out.shape == (rows, 2 * width),
+            "concat_rows: two float32 matrices of one shape and an output twice as wide")
+    _check(lib().citlali_concat_rows(_ptr(a), _ptr(b), _ptr(out), _i(_dtype_code(out)), _i(rows), _i(width), _stream()),
+           "concat_rows")
+
+
 def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
              row_index: Optional[torch.Tensor] = None):
     _need_cuda(x, gain, out, row_index)
@@ -245,14 +262,19 @@ def attention(q, q_stride, cache_view, batch, out, nq, nkv, head_dim, window, sc
 
 
 def attention_prefill(q, q_stride, k_pool, v_pool, page_table, seq_start, seq_slot, seq_past, out, sequences, max_new,
-                      nq, nkv, head_dim, page_size, window, scale, keep_first=0):
+                      nq, nkv, head_dim, page_size, window, scale, keep_first=0, softcap=0.0, gate=None):
+    """``softcap`` c > 0: scaled scores become c tanh(s / c).  ``gate``: float32 [rows, heads * head size] (rows may be
+    further apart than they are long), the output is multiplied by its sigmoids."""
     _need_cuda(k_pool, v_pool, page_table, seq_start, seq_slot, seq_past, out)
     require(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
             "attention_prefill: bfloat16 only")
+    require(gate is None or (gate.is_cuda and gate.dtype == torch.float32 and gate.stride(1) == 1
+                             and gate.shape == (out.shape[0], nq * head_dim)), "attention_prefill: the gate does not fit")
     _check(lib().citlali_attention_prefill(
         _ptr(q), _i(q_stride), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _i(page_table.shape[1]),
         _ptr(seq_start), _ptr(seq_slot), _ptr(seq_past), _ptr(out), _i(out.shape[1]), _i(sequences), _i(max_new),
-        _i(nq), _i(nkv), _i(head_dim), _i(page_size), _i(window or 0), _i(keep_first or 0), _f(scale), _stream()),
+        _i(nq), _i(nkv), _i(head_dim), _i(page_size), _i(window or 0), _i(keep_first or 0), _f(scale),
+        _f(float(softcap or 0.0)), _ptr(gate), _sz(gate.stride(0) if gate is not None else 0), _stream()),
         "attention_prefill")
 
 
@@ -711,56 +733,73 @@ def gated_scan(a, coef, side, side_stride, side_bias, state, state_off, batch, o
 # ---- attention over a window that keeps the first tokens -------------------------------------------------------
 
 def conv_heads_prepare(proj, taps_w, state, conv_off, q_gain, k_gain, inv_freq, rot_dims, batch, kv, q_out, nq, nkv, d, vd,
-                       eps, write_cache=True):
-    """``kv``: the cache view (keys [page, nkv, page_size, d], values [..., vd], page table)."""
-    _need_cuda(proj, taps_w, state, q_gain, k_gain, inv_freq, kv.keys, kv.values, kv.page_table, q_out)
+                       eps, write_cache=True, bias=None):
+    """``kv``: the cache view (keys [page, nkv, page_size, d], values [..., vd], page table).  ``proj`` may be wider than
+    q | k | v (what follows is not looked at).  ``bias``: float32, a number a channel, added ahead of the head norm."""
+    _need_cuda(proj, taps_w, state, q_gain, k_gain, inv_freq, kv.keys, kv.values, kv.page_table, q_out, bias)
     rows = proj.shape[0]
     C = (nq + nkv) * d + nkv * vd
-    require(proj.dtype == torch.float32 and proj.shape[1] == C and taps_w.shape[0] == C and taps_w.dtype == torch.float32
+    require(bias is None or (bias.dtype == torch.float32 and bias.numel() == C), "conv_heads_prepare: the bias does not fit")
+    require(proj.dtype == torch.float32 and proj.shape[1] >= C and taps_w.shape[0] == C and taps_w.dtype == torch.float32
             and q_out.shape == (rows, nq * d) and kv.keys.shape[-1] == d and kv.values.shape[-1] == vd
             and kv.keys.dtype == kv.values.dtype and (rot_dims == 0 or inv_freq.numel() == rot_dims // 2),
             "conv_heads_prepare: shapes or dtypes do not fit")
     _check(lib().citlali_conv_heads_prepare(
-        _ptr(proj), _i(C), _ptr(taps_w), _i(taps_w.shape[1]), _ptr(state), _sz(state.shape[1] if state is not None else 0),
+        _ptr(proj), _i(proj.shape[1]), _ptr(taps_w), _i(taps_w.shape[1]), _ptr(state), _sz(state.shape[1] if state is not None else 0),
         _sz(conv_off), _ptr(q_gain), _ptr(k_gain), _ptr(inv_freq), _i(rot_dims), _ptr(batch.row_slot), _ptr(batch.row_pos),
         _ptr(kv.page_table), _i(kv.page_table.shape[1]), _ptr(kv.keys), _ptr(kv.values), _i(_dtype_code(kv.keys)),
         _i(kv.page_size), _ptr(q_out), _i(_dtype_code(q_out)), _i(rows), _i(nq), _i(nkv), _i(d), _i(vd), _f(eps),
-        _i(1 if write_cache else 0), _stream()), "conv_heads_prepare")
+        _i(1 if write_cache else 0), _ptr(bias), _stream()), "conv_heads_prepare")
 
 
-def attention_window(q, kv, batch, out, nq, nkv, d, vd, window, keep_first, scale):
+def attention_window(q, kv, batch, out, nq, nkv, d, vd, window, keep_first, scale, softcap=0.0, gate=None):
     """Attention of every row over its slot's cache, through a window that keeps the first tokens.  bfloat16 steps that
     bring runs of tokens, with keys and values of one size the tensor-core kernel has, run that kernel; steps of single
-    tokens, the 32-bit path and other sizes run the kernel whose launch depends on the row count alone."""
+    tokens, the 32-bit path and other sizes run the kernel whose launch depends on the row count alone.  ``softcap`` c > 0:
+    the scaled scores become c tanh(s / c).  ``gate``: float32 columns of a matrix (a view whose rows may be further apart
+    than they are long), the output is multiplied by their sigmoids element by element."""
     _need_cuda(q, kv.keys, kv.values, kv.page_table, out)
     rows = q.shape[0]
     require(q.shape == (rows, nq * d) and out.shape == (rows, nq * vd) and q.dtype == out.dtype,
             "attention_window: shapes or dtypes do not fit")
+    gate_stride = 0
+    if gate is not None:
+        require(gate.is_cuda and gate.dtype == torch.float32 and gate.shape == (rows, nq * vd) and gate.stride(1) == 1,
+                "attention_window: the gate is float32 [rows, heads * value size] with unit column stride")
+        gate_stride = gate.stride(0)
+    softcap = float(softcap or 0.0)
     if (q.dtype == torch.bfloat16 and kv.keys.dtype == torch.bfloat16 and d == vd and not batch.is_decode
             and (nq * d) % 8 == 0 and not torch.cuda.is_current_stream_capturing()
+            and (gate is None or (gate_stride % 2 == 0 and gate.data_ptr() % 8 == 0))
             and lib().citlali_attention_prefill_supports(_i(d), _i(kv.page_size))):
         attention_prefill(q, nq * d, kv.keys, kv.values, kv.page_table, batch.seq_start, batch.seq_slot, batch.seq_past, out,
-                          batch.sequences, batch.max_new, nq, nkv, d, kv.page_size, window, scale, keep_first=keep_first)
+                          batch.sequences, batch.max_new, nq, nkv, d, kv.page_size, window, scale, keep_first=keep_first,
+                          softcap=softcap, gate=gate)
         return
     longest = kv.page_table.shape[1] * kv.page_size          # a bound that no step's lengths change
     max_keys = min(longest, window + keep_first) if window else longest
     _check(lib().citlali_attention_window(
         _ptr(q), _i(_dtype_code(q)), _ptr(kv.keys), _ptr(kv.values), _i(_dtype_code(kv.keys)), _ptr(kv.page_table),
         _i(kv.page_table.shape[1]), _ptr(batch.row_slot), _ptr(batch.row_pos), _ptr(out), _i(rows), _i(nq), _i(nkv), _i(d),
-        _i(vd), _i(kv.page_size), _i(int(window or 0)), _i(int(keep_first or 0)), _i(max_keys), _f(scale), _stream()),
-        "attention_window")
+        _i(vd), _i(kv.page_size), _i(int(window or 0)), _i(int(keep_first or 0)), _i(max_keys), _f(scale), _f(softcap),
+        _ptr(gate), _sz(gate_stride), _stream()), "attention_window")
 
 
 # ---- routed experts -----------------------------------------------------------------------------------------------
 
-def moe_route(logits, weights, groups, keep, top, chosen=None, weight_scale=1.0):
+ROUTER_SCORES = {"softmax": 0, "sigmoid": 1}
+
+
+def moe_route(logits, weights, groups, keep, top, chosen=None, weight_scale=1.0, score="softmax"):
     _need_cuda(logits, weights, chosen)
+    require(score in ROUTER_SCORES, f"moe_route: unknown score '{score}'; known: {', '.join(ROUTER_SCORES)}")
     rows, E = logits.shape
     require(logits.dtype == torch.float32 and weights.dtype == torch.float32 and weights.shape == logits.shape
             and (chosen is None or (chosen.dtype == torch.int32 and chosen.shape == (rows, top))),
             "moe_route: shapes or dtypes do not fit")
     _check(lib().citlali_moe_route(_ptr(logits), _ptr(weights), _ptr(chosen), _i(rows), _i(E), _i(int(groups or 0)),
-                                   _i(int(keep or 0)), _i(top), _f(weight_scale), _stream()), "moe_route")
+                                   _i(int(keep or 0)), _i(top), _f(weight_scale), _i(ROUTER_SCORES[score]), _stream()),
+           "moe_route")
 
 
 def moe_scale(act, weights, ff):
@@ -771,13 +810,17 @@ def moe_scale(act, weights, ff):
            "moe_scale")
 
 
-EXPERT_ACTIVATIONS = {"silu": 0, "clamped_swish": 1}
+EXPERT_ACTIVATIONS = {"silu": 0, "clamped_swish": 1, "gelu_tanh": 2}
 
 
-def expert_gate(gate_up, weights, act, E, ff, run, kind, limit=0.0, alpha=1.0, tail_ff=0, tail_run=1, tail_limit=0.0):
+def expert_gate(gate_up, weights, act, E, ff, run, kind, limit=0.0, alpha=1.0, tail_ff=0, tail_run=1, tail_limit=0.0,
+                bias=None, weight_input=False):
     """The gated activation of ``E`` routed experts (times the row's weight for each) and of a last expert that every row
-    uses, from one product ``gate_up`` [rows, 2 (E ff + tail_ff)] into ``act`` [rows, E ff + tail_ff]."""
-    _need_cuda(gate_up, weights, act)
+    uses, from one product ``gate_up`` [rows, 2 (E ff + tail_ff)] into ``act`` [rows, E ff + tail_ff].  ``bias``: float32,
+    a number a column of ``gate_up``, added first.  ``weight_input``: the row's weight multiplies gate and up ahead of
+    the activation (the expert applied to the weighted input) instead of the activation's result."""
+    _need_cuda(gate_up, weights, act, bias)
+    require(bias is None or (bias.dtype == torch.float32 and bias.numel() == gate_up.shape[1]), "expert_gate: the bias does not fit")
     rows = act.shape[0]
     n = E * ff + tail_ff
     require(kind in EXPERT_ACTIVATIONS and act.shape == (rows, n) and gate_up.shape == (rows, 2 * n)
@@ -785,7 +828,8 @@ def expert_gate(gate_up, weights, act, E, ff, run, kind, limit=0.0, alpha=1.0, t
             "expert_gate: shapes or dtypes do not fit")
     _check(lib().citlali_expert_gate(_ptr(gate_up), _i(_dtype_code(gate_up)), _ptr(weights), _ptr(act), _i(_dtype_code(act)),
                                      _i(rows), _i(E), _i(ff), _i(run), _i(EXPERT_ACTIVATIONS[kind]), _f(limit), _f(alpha),
-                                     _i(tail_ff), _i(tail_run), _f(tail_limit), _stream()), "expert_gate")
+                                     _i(tail_ff), _i(tail_run), _f(tail_limit), _ptr(bias), _i(1 if weight_input else 0),
+                                     _stream()), "expert_gate")
 
 
 def bias_xielu(z, bias, ap, an, out):
@@ -887,7 +931,7 @@ def sigmoid_attention_mma(q, kv, batch, talk, head_bias, gate, out, H, G, D, V, 
 # ---- attention through a shared latent -------------------------------------------------------------
 
 def latent_prepare(proj, RQ, R, P, has_kv, q_weight, c_weight, inv_freq, rot_dims, row_slot, row_pos, page_table, pool,
-                   page_size, cq, eps):
+                   page_size, cq, eps, rot_halves=False):
     _need_cuda(proj, q_weight, c_weight, inv_freq, row_slot, row_pos, page_table, pool, cq)
     rows = proj.shape[0]
     require(proj.dtype == torch.float32 and q_weight.dtype == torch.float32 and cq.shape == (rows, RQ)
@@ -900,18 +944,19 @@ def latent_prepare(proj, RQ, R, P, has_kv, q_weight, c_weight, inv_freq, rot_dim
         _ptr(proj), _i(proj.shape[1]), _i(RQ), _i(R), _i(P), _i(1 if has_kv else 0), _ptr(q_weight), _ptr(c_weight),
         _ptr(inv_freq), _i(rot_dims), _ptr(row_slot), _ptr(row_pos), _ptr(page_table), _i(page_table.shape[1]), _ptr(pool),
         _i(_dtype_code(pool) if pool is not None else _F32), _i(page_size), _ptr(cq), _i(_dtype_code(cq)), _i(rows),
-        _f(eps), _stream()), "latent_prepare")
+        _f(eps), _i(1 if rot_halves else 0), _stream()), "latent_prepare")
 
 
 def heads_product(x, x_row, x_head, M, m_head, m_k, m_n, y, y_row, y_head, rows, heads, K, N, tail=0, inv_freq=None,
-                  rot_dims=0, row_pos=None, gate=None, gate_stride=0):
+                  rot_dims=0, row_pos=None, gate=None, gate_stride=0, rot_halves=False, gate_per_head=False):
     """``y[r, h, :N] = x[r, h, :K] . M_h`` with a matrix per head given by strides; see ``citlali_heads_product``."""
     _need_cuda(M, y, inv_freq, row_pos)
     require(x.is_cuda and (gate is None or (gate.is_cuda and gate.dtype == torch.float32)), "heads_product: bad operands")
     _check(lib().citlali_heads_product(
         _ptr(x), _i(_dtype_code(x)), _sz(x_row), _i(x_head), _ptr(M), _i(_dtype_code(M)), _sz(m_head), _i(m_k), _i(m_n),
         _ptr(y), _i(_dtype_code(y)), _sz(y_row), _i(y_head), _i(rows), _i(heads), _i(K), _i(N), _i(tail), _ptr(inv_freq),
-        _i(rot_dims), _ptr(row_pos), _ptr(gate), _sz(gate_stride), _stream()), "heads_product")
+        _i(rot_dims), _ptr(row_pos), _ptr(gate), _sz(gate_stride), _i(1 if rot_halves else 0),
+        _i(1 if gate_per_head else 0), _stream()), "heads_product")
 
 
 _KERNELS_PER_CALL["latent_attention_mma_runs"] = 2

@@ -129,6 +129,11 @@ class StepBatch:
     normed_carry: Optional[tuple] = None
     normed_carry_in: Optional[tuple] = None
     next_first_norm: Optional[object] = None
+    # For blocks that say ``needs_embedding_output``: the rows as the embedding (and its norm, if the model has one) left
+    # them, float32 [rows, hidden], untouched by the layers; and how often the layer that runs now has run before in
+    # this step (a layer the schedule names several times: 0, 1, 2, ...).
+    embedding_output: Optional[torch.Tensor] = None
+    visit: int = 0
 
     @property
     def rows(self) -> int:

@@ -22,7 +22,10 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..errors import require
+from ..weights.loader import TensorSpec
 from .base import NormedRows, build_part, register_part
+from .linear import DenseLinear
 from .norm import RMSNorm
 
 _FEW_ROWS = 128        # up to here the product always runs the form whose epilogue can do a norm's work
@@ -224,6 +227,88 @@ class SandwichNormBlock:
         return x
 
 
+class ParallelResidualBlock:
+    """h = norm(x); x += mixer(h) + feed_forward(h): one norm, and both sub-layers read what it gives.  Parts by name:
+    ``norm``, ``mixer``, ``feed_forward`` (either sub-layer may be absent).  Both outputs are added into the float32
+    residual by the products that end the sub-layers (32-bit additions)."""
+
+    def __init__(self, layer_spec):
+        has = layer_spec.parts.__contains__
+        self.norm = build_part("norm", layer_spec.part("norm"))
+        self.mixer = build_part("mixer", layer_spec.part("mixer")) if has("mixer") else None
+        self.feed_forward = build_part("feed_forward", layer_spec.part("feed_forward")) if has("feed_forward") else None
+
+    def parts(self):
+        return [p for p in (self.norm, self.mixer, self.feed_forward) if p is not None]
+
+    def tensor_specs(self):
+        return [t for p in self.parts() for t in p.tensor_specs()]
+
+    def cache_requirement(self):
+        return self.mixer.cache_requirement() if self.mixer is not None else None
+
+    def bind(self, weights, ctx):
+        for p in self.parts():
+            p.bind(weights, ctx)
+
+    def first_norm(self):
+        return self.norm
+
+    def forward(self, x, batch, cache_view, write_cache=True):
+        h = self.norm.forward(x)
+        if self.mixer is not None:
+            self.mixer.forward(h, batch, cache_view, x, write_cache)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(h, batch, x)
+        return x
+
+
+class InputInjectionBlock:
+    """x <- W [x ; x0] + b_t: the residual is mixed again with the rows the embedding left (x0), by one matrix
+    ``[hidden, 2 hidden]`` whose first half meets x, and a vector is added that depends on how often this block has run
+    in the step (row t of a table ``[passes, hidden]``; a schedule names the block once ahead of every pass over a run of
+    layers that repeats).  No norm, no cache.  The product reads [x ; x0] rounded once to the compute dtype; its result
+    and the sum are float32.  ``block_params``: hidden_size, passes, ``matrix`` and ``steps`` (the tensors' full names)."""
+    needs_embedding_output = True
+    graph_safe = True
+
+    def __init__(self, layer_spec):
+        bp = layer_spec.block_params
+        self.hidden, self.passes = int(bp["hidden_size"]), int(bp["passes"])
+        self.steps_name = str(bp["steps"])
+        self.mix = DenseLinear([str(bp["matrix"])], [self.hidden], 2 * self.hidden)
+
+    def parts(self):
+        return []
+
+    def tensor_specs(self):
+        return self.mix.tensor_specs() + [TensorSpec(self.steps_name, (self.passes, self.hidden), "state")]
+
+    def cache_requirement(self):
+        return None
+
+    def bind(self, weights, ctx):
+        self.mix.bind(weights, ctx)
+        h = weights[self.steps_name]
+        require(tuple(h.shape) == (self.passes, self.hidden),
+                f"unexpected tensor shape for {self.steps_name}: got {list(h.shape)}, expected {[self.passes, self.hidden]}")
+        self.steps = h.tensor.to(device=ctx.device, dtype=torch.float32).contiguous()
+        self.dtype = ctx.dtype
+
+    def forward(self, x, batch, cache_view, write_cache=True):
+        x0 = batch.embedding_output
+        require(x0 is not None and x0.shape == x.shape and x0.data_ptr() != x.data_ptr(),
+                "the injection block needs the embedding's rows beside the residual")
+        require(0 <= batch.visit < self.passes, f"the injection block has run {batch.visit} times, its table has {self.passes} rows")
+        both = torch.empty((x.shape[0], 2 * self.hidden), dtype=self.dtype, device=x.device)
+        ops.concat_rows(x, x0, both)
+        self.mix.forward(both, out=x)
+        ops.add_row_bias(x, self.steps[batch.visit])
+        return x
+
+
+register_part("block", "parallel_residual", ParallelResidualBlock)
+register_part("block", "input_injection", InputInjectionBlock)
 register_part("block", "pre_norm_residual", PreNormResidualBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)
 register_part("block", "sublayer_output_norm", SublayerOutputNormBlock)

@@ -7,19 +7,21 @@ q_plain . (W_uk c) = (W_uk^T q_plain) . c, the heads' matrices are applied to th
 latents after the walk over the cache (``ops.heads_product``), and the walk (``ops.latent_attention``) reads the cached
 vector once for every head.  Scores are scaled by ``scale``; position i sees j with 0 <= i - j < window (None: every
 j <= i); the softmax's denominator also counts exp(sink_a), a learned number per head without key or value (absent
-tensor name: none); the heads side by side are multiplied by sigmoid(W_g h), then pass the output matrix.
+tensor name: none); the heads side by side are multiplied by sigmoid(W_g h), then pass the output matrix.  ``gate``
+"elements" (the default): W_g gives a number for every element of every head's output; "heads": one number a head.
 
 A layer with ``kv_projection`` false has no W_dkv and reads the cache of the layer the model's schedule names; the
 layer that owns a cache keeps it for the widest window among its readers (``cache_window``).
 
 Rotation: pairs (2i, 2i+1), i < rot_dims / 2, of the key part and of each head's q_rot turn by position * base^(-2i /
-rot_dims); the angle is a float32 product of the position and a tabulated frequency.
+rot_dims); the angle is a float32 product of the position and a tabulated frequency.  ``rot_layout`` "halves" pairs
+element i with element i + rot_dims / 2 instead (the first of a pair, u, becomes u cos - v sin, the second v cos + u sin).
 
 The result of W_dq / W_dkv / W_g (one product) and the query are kept in float32; norms, rotation, scores and softmax are
 float32 in both paths.
 
 Parameters: hidden_size, heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, norm_eps, window, cache_window,
-rot_dims, rot_base, kv_projection; ``names``: full tensor names by role (dq, dq_norm, uq, dkv, dkv_norm, uk, uv, sink,
+rot_dims, rot_base, rot_layout, gate, kv_projection; ``names``: full tensor names by role (dq, dq_norm, uq, dkv, dkv_norm, uk, uv, sink,
 gate, o); ``sink`` may be None.
 """
 from __future__ import annotations
@@ -54,6 +56,10 @@ class LatentAttention:
         self.rot_dims = int(params.get("rot_dims") or 0)
         self.rot_base = float(params.get("rot_base") or 1.0)
         self.kv_projection = bool(params.get("kv_projection", True))
+        self.rot_halves = {"pairs": False, "halves": True}.get(str(params.get("rot_layout") or "pairs"))
+        require(self.rot_halves is not None, f"{prefix}: rot_layout must be 'pairs' or 'halves'")
+        self.gate_per_head = {"elements": False, "heads": True}.get(str(params.get("gate") or "elements"))
+        require(self.gate_per_head is not None, f"{prefix}: gate must be 'elements' or 'heads'")
         require(self.window is None or int(self.window) > 0, f"{prefix}: window must be positive or None")
         require(self.rot_dims % 2 == 0 and self.rot_dims <= self.P,
                 f"{prefix}: {self.rot_dims} rotated dimensions must be even and at most the key part's {self.P}")
@@ -65,7 +71,7 @@ class LatentAttention:
         self.prefix = prefix
         nm, hv = self.names, self.H * self.V
         down = [nm["dq"]] + ([nm["dkv"]] if self.kv_projection else []) + [nm["gate"]]
-        outs = [self.RQ] + ([self.R + self.P] if self.kv_projection else []) + [hv]
+        outs = [self.RQ] + ([self.R + self.P] if self.kv_projection else []) + [self.H if self.gate_per_head else hv]
         self.down = DenseLinear(down, outs, self.hidden)
         self.gate_at = sum(outs[:-1])
         self.uq = DenseLinear([nm["uq"]], [self.H * (self.D + self.P)], self.RQ)
@@ -119,17 +125,19 @@ class LatentAttention:
         proj = self.down.forward(h, out_dtype=torch.float32)
         cq = torch.empty((rows, self.RQ), dtype=self.dtype, device=dev)
         ops.latent_prepare(proj, self.RQ, R, P, self.kv_projection, self.q_weight, self.c_weight, self.inv_freq,
-                           self.rot_dims, batch.row_slot, batch.row_pos, table, pool, page, cq, self.eps)
+                           self.rot_dims, batch.row_slot, batch.row_pos, table, pool, page, cq, self.eps,
+                           rot_halves=self.rot_halves)
         q = self.uq.forward(cq, out_dtype=torch.float32)                      # [rows, H (D + P)]
         qa = torch.empty((rows, H * (R + P)), dtype=torch.float32, device=dev)
         ops.heads_product(q, H * (D + P), D + P, self.uk, D * R, R, 1, qa, H * (R + P), R + P, rows, H, D, R,
-                          tail=P, inv_freq=self.inv_freq, rot_dims=self.rot_dims, row_pos=batch.row_pos)
+                          tail=P, inv_freq=self.inv_freq, rot_dims=self.rot_dims, row_pos=batch.row_pos,
+                          rot_halves=self.rot_halves)
         mixed = torch.empty((rows, H * R), dtype=torch.float32, device=dev)
         ops.latent_attention(qa, pool, table, batch.row_slot, batch.row_pos, self.sink, mixed, H, R, R + P, page,
                              int(self.window or 0), self.scale)
         heads = torch.empty((rows, H * V), dtype=self.dtype, device=dev)
         ops.heads_product(mixed, H * R, R, self.uv, V * R, 1, R, heads, H * V, V, rows, H, R, V,
-                          gate=proj[:, self.gate_at:], gate_stride=proj.shape[1])
+                          gate=proj[:, self.gate_at:], gate_stride=proj.shape[1], gate_per_head=self.gate_per_head)
         if overwrite:
             self.o.forward(heads, out=residual)
         else:

@@ -1,10 +1,12 @@
 """Routed experts: a feed-forward made of ``experts`` small gated feed-forwards of which every token uses ``top``.
 
-Router logits z = W_router h in 32-bit; scores s = softmax(z) over all experts.  The experts form ``groups`` equal groups of
+Router logits z = W_router h in 32-bit; scores s = softmax(z) over all experts (``score`` "sigmoid": s = sigmoid(z), every
+expert's score by itself).  The experts form ``groups`` equal groups of
 neighbours; a group's score is the largest score in it, and only experts of the ``keep_groups`` best groups can be chosen
 (``groups`` None: no groups).  The ``top`` experts with the largest scores among those are chosen; their weights are their
 scores times ``weight_scale``, not renormalised.  An expert is  W_down act(W_gate h, W_up h), without biases; the output is
-the weighted sum of the chosen experts' outputs.  ``activation``:
+the weighted sum of the chosen experts' outputs, or with ``weight_on`` "input" the sum of the experts applied to the weight
+times h (the weight then meets gate and up ahead of the activation: act(w W_gate h, w W_up h)).  ``activation``:
 
 * ``silu`` (the default): act(g, u) = silu(g) u;
 * ``clamped_swish``: g' = min(g, limit), u' = clamp(u, -limit, limit); act = g' sigmoid(alpha g') (u' + 1), with ``limit``
@@ -20,8 +22,8 @@ activation), every expert's activations are multiplied by the row's weight for i
 by side are ONE product that sums over experts.  Nothing depends on counts known to the host
 only, so a decoding step replays as a graph; the price is that every expert's matrices are applied to every row.
 
-Parameters: hidden_size, experts, top, intermediate_size, groups, keep_groups, weight_scale, activation, limit, alpha,
-shared; ``names``: {"router": name, "gate": [names], "up": [names], "down": [names], "shared": {"gate", "up", "down"}}
+Parameters: hidden_size, experts, top, intermediate_size, groups, keep_groups, weight_scale, score, weight_on, activation,
+limit, alpha, shared; ``names``: {"router": name, "gate": [names], "up": [names], "down": [names], "shared": {"gate", "up", "down"}}
 (default ``<prefix>.router``, ``<prefix>.e<i>.{gate,up,down}`` and ``<prefix>.shared.{gate,up,down}``).
 """
 from __future__ import annotations
@@ -50,12 +52,16 @@ class RoutedExperts:
             require(1 <= self.keep <= self.groups and self.keep * (self.E // self.groups) >= self.top,
                     f"{prefix}: {self.keep} groups of {self.E // self.groups} experts cannot give {self.top} experts")
         self.weight_scale = 1.0 if params.get("weight_scale") is None else float(params["weight_scale"])
+        self.score = str(params.get("score") or "softmax")
+        require(self.score in ops.ROUTER_SCORES, f"{prefix}: unknown router score '{self.score}'; known: {', '.join(ops.ROUTER_SCORES)}")
+        self.weight_input = {"output": False, "input": True}.get(str(params.get("weight_on") or "output"))
+        require(self.weight_input is not None, f"{prefix}: weight_on must be 'output' or 'input'")
         self.activation = str(params.get("activation") or "silu")
         require(self.activation in ops.EXPERT_ACTIVATIONS,
                 f"{prefix}: unknown expert activation '{self.activation}'; known: {', '.join(ops.EXPERT_ACTIVATIONS)}")
         self.limit = float(params.get("limit") or 0.0)
         self.alpha = 1.702 if params.get("alpha") is None else float(params["alpha"])
-        require(self.activation == "silu" or self.limit > 0.0, f"{prefix}: the clamped activation needs a positive limit")
+        require(self.activation != "clamped_swish" or self.limit > 0.0, f"{prefix}: the clamped activation needs a positive limit")
         n = dict(params.get("names") or {})
         each = lambda role: list(n.get(role) or [f"{prefix}.e{i}.{role}" for i in range(self.E)])
         shared = params.get("shared")
@@ -64,7 +70,7 @@ class RoutedExperts:
         if shared is not None:
             self.shared_ff = int(shared["intermediate_size"])
             self.shared_limit = float(shared.get("limit") or 0.0)
-            require(self.shared_ff > 0 and (self.activation == "silu" or self.shared_limit > 0.0),
+            require(self.shared_ff > 0 and (self.activation != "clamped_swish" or self.shared_limit > 0.0),
                     f"{prefix}: the expert for every row needs a width and, with the clamped activation, a positive limit")
             sn = dict(n.get("shared") or {})
             name = lambda role: str(sn.get(role) or f"{prefix}.shared.{role}")
@@ -75,7 +81,7 @@ class RoutedExperts:
         self.down = ExpertDown(each("down"), self.ff, self.hidden, tail=down_tail)
         self.prefix = prefix
         # the product's own gate epilogue and the scaling kernel serve the plain form; anything else runs the gate kernel
-        self.plain = self.activation == "silu" and shared is None
+        self.plain = self.activation == "silu" and shared is None and not self.weight_input
 
     def tensor_specs(self):
         return self.router.tensor_specs() + self.gate_up.tensor_specs() + self.down.tensor_specs()
@@ -90,7 +96,7 @@ class RoutedExperts:
         """The row's weights for every expert, float32 [rows, experts]: its score where chosen, zero elsewhere."""
         logits = self.router.forward(h, out_dtype=torch.float32)
         weights = torch.empty_like(logits)
-        ops.moe_route(logits, weights, self.groups, self.keep, self.top, weight_scale=self.weight_scale)
+        ops.moe_route(logits, weights, self.groups, self.keep, self.top, weight_scale=self.weight_scale, score=self.score)
         return weights
 
     def forward(self, h, batch, residual, overwrite=False):
@@ -105,7 +111,7 @@ class RoutedExperts:
             gu = self.gate_up.forward(h, out_dtype=torch.float32)
             act = torch.empty((h.shape[0], self.E * self.ff + self.shared_ff), dtype=self.dtype, device=h.device)
             ops.expert_gate(gu, weights, act, self.E, self.ff, self.gate_up.run, self.activation, self.limit, self.alpha,
-                            self.shared_ff, self.gate_up.tail_run, self.shared_limit)
+                            self.shared_ff, self.gate_up.tail_run, self.shared_limit, weight_input=self.weight_input)
         if overwrite:
             self.down.forward(act, out=residual)
         else:

@@ -43,9 +43,11 @@ class RMSNorm:
         self.gain_downstream = True
         return gain
 
-    def forward(self, x: torch.Tensor, row_index=None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, row_index=None, out_dtype=None) -> torch.Tensor:
+        """``out_dtype``: float32 for rows that stay part of the 32-bit residual (a norm on the embedding's rows);
+        default: the compute dtype, for rows a product reads."""
         rows = x.shape[0] if row_index is None else row_index.numel()
-        out = torch.empty((rows, self.size), dtype=self.dtype, device=x.device)
+        out = torch.empty((rows, self.size), dtype=out_dtype or self.dtype, device=x.device)
         ops.rms_norm(x, self.gain, self.eps, out, row_index)
         return out
 

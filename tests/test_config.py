@@ -66,7 +66,7 @@ def test_required_keys(key):
 
 
 def test_registry_names_its_architectures_and_lists_them_on_a_miss():
-    assert cb.registered_architectures() == ["Gidirax", "Lanizen", "Qwen3ForCausalLM", "Sobunex"]
+    assert cb.registered_architectures() == ["Gidirax", "Lanizen", "Pivavik", "Qwen3ForCausalLM", "Sobunex"]
     with pytest.raises(cb.CitlaliError, match="unknown architecture 'LlamaForCausalLM'.*Qwen3ForCausalLM"):
         cb.config_from_dict(dict(TINY["A"], architectures=["LlamaForCausalLM"]))
     with pytest.raises(cb.CitlaliError, match="architectures"):
