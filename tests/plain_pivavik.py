@@ -117,7 +117,7 @@ def window_attention(h, w, p, m, store=None):
     q, k, v = lin("q").view(T, H, D), lin("k").view(T, G, D), lin("v").view(T, G, V)
     if store is not None:
         k, v = store(k), store(v)
-    mask = causal(T, m["mask"]["size"])
+    mask = causal(T, m["mask"]["size"] if m.get("mask") is not None else None)
     o = torch.empty(T, H, V, dtype=F)
     for hd in range(H):
         g = hd // (H // G)

@@ -1,0 +1,195 @@
+"""The Pivavik decoder through the session, the cache and the step function, against the plain implementation: whole
+prompts; prompts with their tails decoded token by token; every token alone from the first; portions of 2 to 40 tokens and
+of exactly two; batches of unequal requests over few slots and few pages (slots and pages are used again); requests that
+join a running batch; long decoding past every window and over several pages, with layers that run several times over and
+keep a cache every time; bin/trace_run; greedy generation through ``generate`` (whose decode steps are replayed CUDA graphs)
+and the command line.  In 32-bit every way of cutting a sequence must agree with the exact evaluation to rounding; in
+bfloat16 within the rounding of 8-bit mantissas."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import citlali_b200 as cb
+import plain_pivavik as plain
+import replay
+from pivavik_models import CONFIGS, write_model
+from helpers import random_tokens
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"P": [1, 2, 5, 9, 10, 21, 64, 65, 150], "Q": [3, 40, 129, 7, 70, 66], "R": [64, 65, 66, 131, 200, 1, 33],
+           "S": [2, 90, 17, 64, 130]}
+TOL = {"float32": 2e-5, "bfloat16": 5e-2}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("pivavik")
+    out = {}
+    for i, name in enumerate(CONFIGS):
+        path = str(root / name)
+        cfg, w = write_model(path, name, seed=70 + i)
+        out[name] = (path, cfg.to_dict(), w)
+    return out
+
+
+def requests_for(name):
+    return [(f"r{i}", random_tokens(CONFIGS[name]["vocab"], n, 29 * i + n)) for i, n in enumerate(LENGTHS[name])]
+
+
+_plain = {}
+
+
+def plain_rows(models, name):
+    if name not in _plain:
+        _, cfg, w = models[name]
+        _plain[name] = {rid: plain.forward(cfg, w, toks) for rid, toks in requests_for(name)}
+    return _plain[name]
+
+
+def session_for(models, name, dtype, max_batch=8, max_tokens=None, graphs=True):
+    s = cb.InferenceSession()
+    s.use_graphs = graphs
+    return s.load_model(models[name][0], max_context=1024, dtype=dtype, max_batch=max_batch, max_tokens=max_tokens)
+
+
+# In bfloat16 a router's close call may fall the other way than in the exact evaluation (the rows it reads carry the
+# rounding of everything before them); the token then runs other experts, and through the keys and values it leaves the
+# rows behind it differ too.  The 32-bit path is held to the plain implementation at every position; the bfloat16 path at
+# most of them, and its ways of cutting a sequence are held to one another.
+MOST = {"float32": 1.0, "bfloat16": 0.7}
+
+
+def row_error(row, ref):
+    """The root mean square over the vocabulary of the difference, its mean taken off (a shift of all logits changes no
+    probability), relative to the logits' own spread."""
+    d = row.double() - ref.double()
+    return float((d - d.mean()).pow(2).mean().sqrt() / (ref.double() - ref.double().mean()).pow(2).mean().sqrt())
+
+
+def check(got, want_rows, dtype, what, most=None):
+    worst, good = 0.0, 0
+    for (rid, pos), row in got.items():
+        err = row_error(row, want_rows[rid][pos])
+        if err <= TOL[dtype]:
+            good += 1
+            worst = max(worst, err)
+        else:
+            assert dtype != "float32", f"{what}: request {rid} position {pos}: error {err:.3e}"
+    most = MOST[dtype] if most is None else most
+    assert good >= most * len(got), f"{what}: only {good} of {len(got)} positions agree"
+    print(f"[{what}] {good} of {len(got)} positions agree; worst error among them = {worst:.3e}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_every_way_of_cutting_agrees_with_plain(models, name, dtype):
+    want = plain_rows(models, name)
+    reqs = requests_for(name)
+    s = session_for(models, name, dtype, max_batch=3, max_tokens=512)
+    ways = {
+        "whole": replay.whole(reqs),
+        "tail": replay.tail(reqs, last=32),
+        "token by token": replay.tail(reqs, last=10 ** 6),
+        "portions": replay.chunked(reqs, 3, seed=5, low=2, high=40),
+        "portions of two": replay.chunked(reqs, 2, seed=6, low=2, high=2),
+        "batched": replay.batched(reqs, [max(1, len(t) * 2 // 3) for _, t in reqs], 3),
+        "joining": replay.joining(reqs[:3], [max(1, len(t) // 2) for _, t in reqs[:3]], every=2),
+    }
+    results = {}
+    for what, steps in ways.items():
+        results[what] = replay.run_in_process(s, steps)
+        check(results[what], want, dtype, f"{name} {dtype} {what}")
+        assert s.cache.pages_held() == 0 and s.cache.slots.held == []
+    # one order of operations for every cut: in 32-bit the walk over the cache and the products give the same bits
+    # however a sequence came in
+    base = results["whole"]
+    if dtype == "float32":
+        for what in ("tail", "token by token", "portions", "portions of two", "batched"):
+            for key, row in results[what].items():
+                assert torch.equal(row, base[key]), f"{name}: '{what}' differs from 'whole' at {key}"
+    else:
+        rows = {}
+        for (rid, pos), row in base.items():
+            rows.setdefault(rid, {})[pos] = row
+        for what in ("tail", "token by token", "portions", "portions of two", "batched", "joining"):
+            check(results[what], rows, dtype, f"{name} {dtype} {what} against whole", most=0.9)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_past_windows_and_pages(models, dtype):
+    """A short prompt, then 300 tokens one by one: the windows (9, 65, 130, 1, 64) pass over decoded tokens only; the
+    latent layers keep every token, every time they run."""
+    for name in ("P", "R", "S"):
+        _, cfg, w = models[name]
+        toks = random_tokens(CONFIGS[name]["vocab"], 305, 78)
+        s = session_for(models, name, dtype, max_batch=1, max_tokens=320)
+        check(replay.run_in_process(s, replay.tail([("x", toks)], last=300)), {"x": plain.forward(cfg, w, toks)}, dtype,
+              f"{name} {dtype} long decoding")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(models, dtype):
+    name = "P"
+    reqs = requests_for(name)[2:7]
+    steps = replay.batched(reqs, [max(1, len(t) - 3) for _, t in reqs], 3)
+    got = replay.run_trace_run(models[name][0], dtype, steps, CONFIGS[name]["vocab"])
+    check(got, plain_rows(models, name), dtype, f"trace_run {dtype}")
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("name", ["P", "R"])
+def test_greedy_generation_follows_plain(models, name, graphs):
+    """``generate`` with temperature 0 in 32-bit: every generated token is the plain implementation's choice on the same
+    prefix, unless its margin there is within rounding.  Five prompts over two slots: slots and pages are used again, and the decode steps are replayed graphs (or plain launches)."""
+    _, cfg, w = models[name]
+    s = session_for(models, name, "float32", max_batch=2, graphs=graphs)
+    assert (s.runner is not None) == graphs
+    prompts = [random_tokens(CONFIGS[name]["vocab"], n, 9 * n) for n in (3, 17, 1, 66, 30)]
+    results = s.generate(prompts, cb.GenerationOptions(max_new_tokens=24, temperature=0.0))
+    compared = 0
+    for prompt, res in zip(prompts, results):
+        assert len(res.tokens) == 24
+        logits = plain.forward(cfg, w, list(prompt) + list(res.tokens))
+        for i, tok in enumerate(res.tokens):
+            row = logits[len(prompt) - 1 + i]
+            top = torch.topk(row, 2).values
+            if float(top[0] - top[1]) > 1e-4 * float(row.abs().max()):
+                assert int(row.argmax()) == tok, f"{name}: token {i} of a prompt of {len(prompt)}"
+                compared += 1
+    assert compared >= 100
+
+
+def test_graph_replay_equals_plain_launches_in_bfloat16(models):
+    """The replayed decode step and the same step with plain launches give the same tokens."""
+    name = "P"
+    prompts = [random_tokens(CONFIGS[name]["vocab"], n, 5 * n) for n in (4, 70, 23)]
+    outs = []
+    for graphs in (True, False):
+        s = session_for(models, name, "bfloat16", max_batch=3, graphs=graphs)
+        outs.append([r.tokens for r in s.generate(prompts, cb.GenerationOptions(max_new_tokens=20, temperature=0.0))])
+    assert outs[0] == outs[1]
+
+
+def test_command_line(models):
+    """bin/citlali_cli on a Pivavik folder: the same tokens as ``generate``, and --info from the configuration alone."""
+    cli = os.path.join(replay.ROOT, "bin", "citlali_cli")
+    path = models["P"][0]
+    out = subprocess.run([sys.executable, cli, "--model", path, "--prompt-ids", "1,2,3,4,5", "--prompt-ids", "9,8,7",
+                          "--max-new-tokens", "6", "--ctx", "64", "--dtype", "float32", "--json"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    data = json.loads(out.stdout)
+    session = cb.InferenceSession().load_model(path, max_context=64, dtype="float32", max_batch=8)
+    want = session.generate([[1, 2, 3, 4, 5], [9, 8, 7]], cb.GenerationOptions(max_new_tokens=6, max_context=64))
+    assert [r["tokens"] for r in data["results"]] == [r.tokens for r in want]
+    info = subprocess.run([sys.executable, cli, "--model", path, "--info"], capture_output=True, text=True, timeout=120)
+    assert info.returncode == 0 and "architecture: Pivavik" in info.stdout
+    # an attention layer keeps keys and values of its key/value heads, a latent layer its latent and the shared key part,
+    # and the two layers of the repeated run do so once a pass
+    per_token = 2 * (16 + 24) + 2 * ((48 + 8) + 1 * (40 + 8)) + (32 + 24)
+    assert "cache bytes per token (bfloat16): %d" % (2 * per_token) in info.stdout
