@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload 3|4 [--repetitions R]      the batch workloads of BASELINE.json's other shapes
-    python bench.py --design lanizen|gidirax|sobunex [--sizes small,medium,large]   a design beside another at equal size
+    python bench.py --design lanizen|gidirax|sobunex|pivavik [--sizes small,medium,large]   a design beside another at equal size
 
 Prints ONE JSON line.  For each batch size (8, and 1 and 64 unless --skip-points) the run is a real one: the
 prompts (2,048 random tokens each) are prefilled in one step, then every sequence is decoded token by token up
@@ -319,7 +319,7 @@ class ClockSampler:
 
 def run_design(args):
     """``--design``: a design beside another of the library's at equal width and depth (Lanizen beside the Qwen3 decoder,
-    Gidirax beside Lanizen, Sobunex beside Gidirax; see ``citlali_b200.measure``).  One JSON line; the default workload and its line are not touched."""
+    Gidirax beside Lanizen, Sobunex beside Gidirax, Pivavik beside Sobunex; see ``citlali_b200.measure``).  One JSON line; the default workload and its line are not touched."""
     import citlali_b200  # noqa: F401  (loads the package under its importable name)
     from citlali_b200 import measure
     sizes = [s for s in args.sizes.split(",") if s]
@@ -357,7 +357,7 @@ def main():
     ap.add_argument("--run-from", type=int, default=None,
                     help="length of the prompts of the decode runs (default: the prefill length, 2,048); close to the context "
                          "length it makes a short run, as a profiler capture needs")
-    ap.add_argument("--design", default=None, choices=["lanizen", "gidirax", "sobunex"],
+    ap.add_argument("--design", default=None, choices=["lanizen", "gidirax", "sobunex", "pivavik"],
                     help="measure this design beside the library's closest other design at equal sizes (prompt step, decode "
                          "step, every kernel of both) instead of the benchmark configuration")
     ap.add_argument("--sizes", default="medium,large", help="with --design: which of small, medium, large")

@@ -3,7 +3,8 @@
 Used by ``bench.py --design lanizen`` (beside the Qwen3 dense decoder), ``--design gidirax`` (beside Lanizen, the
 closest design the library has: both mix delta-rule layers with windowed attention) and ``--design sobunex`` (beside
 Gidirax: both have windowed attention with key and value sizes of their own, layer norms on the sub-layers' outputs and
-experts whose weights are not renormalised).  A size is a width and a number of layers; both models get that width, that
+experts whose weights are not renormalised) and ``--design pivavik`` (beside Sobunex: both are made of attention layers
+only, with windows, output gates, biases, and dense and routed feed-forwards in turn).  A size is a width and a number of layers; both models get that width, that
 many layers, feed-forwards of equal parameter count (8 width^2: two matrices of 4 width, or three of 8/3 width) and
 the same vocabulary, with random weights in bfloat16.  Measured per model: one prompt in one step (tokens a second),
 one decode step of ``batch`` sequences at ``context`` through the session's ``decode`` (the replayed graph where the
@@ -78,6 +79,29 @@ def sobunex_config(width: int, layers: int, vocab: int, window: int = 1024):
     for i in range(layers):
         out.append(own if i % 2 == 0 else {"type": "attention", "mixer": dict(mixer, kv_from=i - 1), "mlp": moe})
     return config_from_dict({"architecture": "Sobunex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": out})
+
+
+def pivavik_config(width: int, layers: int, vocab: int, window: int = 1024):
+    """Latent-attention and windowed-attention layers in turn, heads of 128 (latent layers: 128 unrotated + 64 rotated
+    elements a head, a latent of 512); dense feed-forwards of 8/3 width (three matrices: 8 width^2 parameters) and sixteen
+    experts of which a token uses four (about 8 width^2 in all experts of a layer) in turn, so that each kind of mixer meets
+    each kind of feed-forward.  The middle layers are a repeated run that runs once: the step ahead of it is measured, and
+    the model runs as many layers as the design beside it."""
+    heads = max(1, width // 128)
+    ff = max(64, (width // 6 + 32) // 64 * 64)
+    dense = {"kind": "dense", "ff": (8 * width // 3 + 255) // 256 * 256}
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": 16, "top": 4}}
+    latent = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": max(256, width * 3 // 8), "kv_rank": 512,
+              "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
+    attention = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+                 "mask": {"size": window}}
+    order = [("latent_attention", latent, dense), ("attention", attention, moe), ("latent_attention", latent, moe),
+             ("attention", attention, dense)]
+    out = [{"type": t, "mixer": dict(m), "mlp": dict(f)} for t, m, f in (order[i % 4] for i in range(layers))]
+    d = {"architecture": "Pivavik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "layers": out}
+    if layers >= 3:
+        d["loop"] = {"start": 1, "stop": layers - 1, "times": 1}
+    return config_from_dict(d)
 
 
 def qwen3_config(width: int, layers: int, vocab: int):
@@ -209,7 +233,7 @@ def measure_model(config, prompt_tokens: int, batch: int, context: int, steps: i
 
 
 DESIGNS = {"lanizen": (lanizen_config, "qwen3"), "gidirax": (gidirax_config, "lanizen"), "sobunex": (sobunex_config, "gidirax"),
-           "qwen3": (qwen3_config, None)}
+           "pivavik": (pivavik_config, "sobunex"), "qwen3": (qwen3_config, None)}
 
 
 def run(design: str, sizes, prompt_tokens: int, batch: int, context: int, steps: int, warmup: int) -> dict:
