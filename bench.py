@@ -271,7 +271,7 @@ def run_reference(args):
 class ClockSampler:
     """nvidia-smi in the background while something is timed."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,utilization.gpu")
 
     def __init__(self):
         self.proc = None
@@ -295,7 +295,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, busy, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         try:
             for line in open(self.path):
@@ -309,11 +309,19 @@ class ClockSampler:
                 for name, v in zip(names, f[2:6]):
                     if v.lower().startswith("active"):
                         reasons.add(name)
+                try:                                     # samples taken while kernels ran (a short run is mostly host work)
+                    if len(f) > 6 and float(f[6]) >= 50.0:
+                        busy.append(sm[-1])
+                except ValueError:
+                    pass
             os.remove(self.path)
         except Exception:
             pass
         if sm:
             out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+            if busy:
+                out["sm_mhz_busy"] = statistics.median(busy)
+                out["busy_samples"] = len(busy)
         return out
 
 

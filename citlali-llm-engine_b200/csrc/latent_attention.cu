@@ -256,15 +256,29 @@ heads_product_mma_kernel(const TX* __restrict__ x, size_t x_row, int x_head, con
         }
         __syncthreads();
     }
+    // a lane holds two neighbouring columns of a row: stored as one word where the output's rows and heads start on even
+    // elements (8 bytes of float32, 4 of bfloat16)
+    const bool pairs = y_row % 2 == 0 && y_head % 2 == 0 && (reinterpret_cast<uintptr_t>(y) & (2 * sizeof(TY) - 1)) == 0;
 #pragma unroll
     for (int n = 0; n < 8; ++n)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int row = row0 + warp * 16 + g + (c >> 1) * 8, col = n0 + n * 8 + t * 2 + (c & 1);
+        for (int half = 0; half < 2; ++half) {
+            const int row = row0 + warp * 16 + g + half * 8, col = n0 + n * 8 + t * 2;
             if (row >= rows || col >= N) continue;
-            float v = acc[n][c];
-            if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)row * gate_stride + (gate_per_head ? (size_t)h : (size_t)h * N + col)]));
-            stf(y, (size_t)row * y_row + (size_t)h * y_head + col, v);
+            float v0 = acc[n][2 * half], v1 = acc[n][2 * half + 1];
+            if (gate) {
+                const float* gr = gate + (size_t)row * gate_stride + (gate_per_head ? (size_t)h : (size_t)h * N + col);
+                v0 *= 1.0f / (1.0f + expf(-gr[0]));
+                if (col + 1 < N) v1 *= 1.0f / (1.0f + expf(-gr[gate_per_head ? 0 : 1]));
+            }
+            TY* dst = y + (size_t)row * y_row + (size_t)h * y_head + col;
+            if (pairs && col + 1 < N) {
+                if constexpr (sizeof(TY) == 4) *reinterpret_cast<float2*>(dst) = make_float2(v0, v1);
+                else *reinterpret_cast<uint32_t*>(dst) = fa::pack_bf16(v0, v1);
+            } else {
+                stf(dst, 0, v0);
+                if (col + 1 < N) stf(dst, 1, v1);
+            }
         }
     if (tail > 0 && blockIdx.z == 0)
         rotate_tail(x, x_row, x_head, y, y_row, y_head, h, row0, 64, rows, K, N, tail, inv_freq, rot_dims, row_pos, rot_halves);

@@ -102,12 +102,15 @@ class LatentAttention:
         self.q_weight = bind_float32(weights, nm["dq_norm"], (self.RQ,), ctx)
         self.c_weight = bind_float32(weights, nm["dkv_norm"], (self.R,), ctx) if self.kv_projection else None
         self.sink = bind_float32(weights, nm["sink"], (self.H,), ctx) if nm["sink"] is not None else None
-        self.uk = torch.empty((self.H * self.D, self.R), dtype=ctx.dtype, device=ctx.device)
+        uk = torch.empty((self.H * self.D, self.R), dtype=ctx.dtype, device=ctx.device)
         self.uv = torch.empty((self.H * self.V, self.R), dtype=ctx.dtype, device=ctx.device)
-        for name, dst in ((nm["uk"], self.uk), (nm["uv"], self.uv)):
+        for name, dst in ((nm["uk"], uk), (nm["uv"], self.uv)):
             require(tuple(weights[name].shape) == tuple(dst.shape),
                     f"unexpected tensor shape for {name}: got {list(weights[name].shape)}, expected {list(dst.shape)}")
             weights[name].copy_into(dst)
+        # W_uk meets the query along its rows (sum over a head's D rows): kept [head, R, D], so that both per-head products
+        # read their matrices along the axis they sum over, in 16-byte pieces
+        self.uk = uk.view(self.H, self.D, self.R).transpose(1, 2).contiguous()
         i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
         self.inv_freq = (torch.pow(torch.tensor(self.rot_base, dtype=torch.float64), -2.0 * i / max(self.rot_dims, 1))
                          .to(torch.float32).to(ctx.device)) if self.rot_dims else None
@@ -129,7 +132,7 @@ class LatentAttention:
                            rot_halves=self.rot_halves)
         q = self.uq.forward(cq, out_dtype=torch.float32)                      # [rows, H (D + P)]
         qa = torch.empty((rows, H * (R + P)), dtype=torch.float32, device=dev)
-        ops.heads_product(q, H * (D + P), D + P, self.uk, D * R, R, 1, qa, H * (R + P), R + P, rows, H, D, R,
+        ops.heads_product(q, H * (D + P), D + P, self.uk, D * R, 1, D, qa, H * (R + P), R + P, rows, H, D, R,
                           tail=P, inv_freq=self.inv_freq, rot_dims=self.rot_dims, row_pos=batch.row_pos,
                           rot_halves=self.rot_halves)
         mixed = torch.empty((rows, H * R), dtype=torch.float32, device=dev)
