@@ -73,17 +73,30 @@ __global__ void soft_cap_kernel(float* __restrict__ x, size_t n, float cap, floa
         x[i] = cap * tanhf(x[i] * inv_cap);
 }
 
-// out[r] = [a[r] | b[r]] (two float32 matrices of `width` columns side by side), rounded once to out's type.
-template <typename TO>
+// out[r] = [a[r] | b[r]] (two float32 matrices of `width` columns side by side), rounded once to out's type.  VEC: four
+// neighbouring columns a thread (width a multiple of four, 16-byte aligned rows).
+template <typename TO, bool VEC>
 __global__ void concat_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, TO* __restrict__ out, size_t rows,
                                    int width) {
     dependents_may_launch();
     wait_for_predecessor();
-    const size_t n = rows * 2 * (size_t)width;
+    constexpr int PER = VEC ? 4 : 1;
+    const size_t n = rows * 2 * (size_t)width / PER;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t r = i / (2 * (size_t)width);
-        const int c = (int)(i % (2 * (size_t)width));
-        stf(out, i, c < width ? a[r * width + c] : b[r * width + c - width]);
+        const size_t e = i * PER, r = e / (2 * (size_t)width);
+        const int c = (int)(e % (2 * (size_t)width));
+        const float* src = c < width ? a + r * width + c : b + r * width + c - width;
+        if constexpr (VEC) {
+            const float4 v = *reinterpret_cast<const float4*>(src);
+            if constexpr (sizeof(TO) == 2) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                *reinterpret_cast<uint2*>(out + e) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+            } else {
+                *reinterpret_cast<float4*>(out + e) = v;
+            }
+        } else {
+            stf(out, e, src[0]);
+        }
     }
 }
 
@@ -238,9 +251,12 @@ extern "C" int citlali_soft_cap(float* x, size_t n, float cap, cudaStream_t stre
 extern "C" int citlali_concat_rows(const float* a, const float* b, void* out, int out_dtype, int rows, int width,
                                    cudaStream_t stream) {
     if (rows <= 0 || width <= 0) return 0;
-    const size_t n = (size_t)rows * 2 * width, blocks = (n + 255) / 256;
+    const bool vec = width % 4 == 0 && (((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15u) == 0;
+    const size_t n = (size_t)rows * 2 * width / (vec ? 4 : 1), blocks = (n + 255) / 256;
+    const int grid = (int)(blocks < 8192 ? blocks : 8192);
     return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
-        launch_kernel(concat_rows_kernel<TO>, (int)(blocks < 8192 ? blocks : 8192), 256, 0, stream, a, b, (TO*)out, (size_t)rows, width);
+        if (vec) launch_kernel(concat_rows_kernel<TO, true>, grid, 256, 0, stream, a, b, (TO*)out, (size_t)rows, width);
+        else launch_kernel(concat_rows_kernel<TO, false>, grid, 256, 0, stream, a, b, (TO*)out, (size_t)rows, width);
         return CITLALI_LAUNCH_CHECK();
     });
 }

@@ -468,8 +468,13 @@ def test_soft_cap_and_concat_kernels():
     y = x.to(DEV).clone()
     ops.soft_cap_(y, 30.0)
     assert float((y.double().cpu() - plain.soft_cap(x.double(), 30.0)).abs().max()) < 1e-5
-    a, b = torch.randn(7, 10), torch.randn(7, 10)
-    for dtype in DTYPES:
-        out = torch.empty(7, 20, dtype=dtype, device=DEV)
-        ops.concat_rows(a.to(DEV), b.to(DEV), out)
-        assert torch.equal(out.cpu(), torch.cat([a, b], -1).to(dtype))
+    for width in (10, 12, 64, 200):                       # rows that are and are not multiples of four floats
+        a, b = torch.randn(7, width), torch.randn(7, width)
+        for dtype in DTYPES:
+            out = torch.empty(7, 2 * width, dtype=dtype, device=DEV)
+            ops.concat_rows(a.to(DEV), b.to(DEV), out)
+            assert torch.equal(out.cpu(), torch.cat([a, b], -1).to(dtype))
+        table = torch.randn(3, width)
+        y = a.to(DEV).clone()
+        ops.add_row_bias(y, table.to(DEV)[2])
+        assert torch.equal(y.cpu(), a + table[2])
