@@ -64,7 +64,7 @@ CONFIGS = {
     # of 64 and of 32 with equal key and value sizes); windows of several pages and of one token; sixteen experts
     "R": model(512, 96, 1e-6, 25.0, (0, 4, 2), [
         att(8, 2, 64, 64, 0.125, 10.0, 130, moe(16, 4, 16)),
-        lat(6, 32, 16, 32, 48, 64, 0.15, 250000.0, dense(200)),
+        lat(5, 32, 16, 32, 48, 64, 0.15, 200000.0, dense(200)),
         att(2, 2, 32, 32, 0.2, 4.0, 1, dense(64)),
         lat(16, 16, 16, 16, 64, 64, 0.2, 10000.0, dense(80))]),
     # the repeated run reaches the last layer and runs three times; attention layers only inside it; no window on one of them

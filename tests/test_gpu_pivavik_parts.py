@@ -160,7 +160,7 @@ def latent_config(p):
 LATENT = [
     latent_params(40, 3, 16, 8, 24, 24, 48, 0.2, 10000.0),                 # a rotated part smaller than the rest
     latent_params(48, 5, 12, 20, 12, 36, 44, 0.25, 100.0, rot_dims=12),    # only 12 of 20 elements turn; odd sizes
-    latent_params(64, 16, 16, 16, 32, 64, 64, 0.2, 250000.0),              # sizes the tensor-core walk takes, sixteen heads
+    latent_params(64, 16, 16, 16, 32, 64, 64, 0.2, 200000.0),              # sizes the tensor-core walk takes, sixteen heads
     latent_params(32, 1, 8, 32, 8, 16, 128, 0.15, 500.0),                  # one head; the rotated part carries the score
     latent_params(64, 20, 32, 64, 16, 32, 128, 0.1, 10000.0),              # more heads than one tile of the walk holds
 ]
@@ -368,7 +368,7 @@ def test_gelu_feed_forward_with_biases(hidden, ff, dtype):
     close(y.double().cpu(), want, dtype, f"{dtype} overwrite")
 
 
-@pytest.mark.parametrize("experts,top", [(6, 2), (3, 3), (16, 4), (12, 1), (40, 5)])
+@pytest.mark.parametrize("experts,top", [(6, 2), (3, 3), (16, 4), (10, 1), (40, 5)])
 def test_sigmoid_router(experts, top):
     g = torch.Generator().manual_seed(experts)
     logits = (3.0 * torch.randn(50, experts, generator=g)).float()
@@ -386,7 +386,7 @@ def test_sigmoid_router(experts, top):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden,experts,top,ff", [(40, 6, 2, 32), (60, 3, 3, 24), (64, 16, 4, 16), (32, 12, 1, 40)])
+@pytest.mark.parametrize("hidden,experts,top,ff", [(40, 6, 2, 32), (60, 3, 3, 24), (64, 16, 4, 16), (32, 10, 1, 40)])
 def test_experts_that_read_their_weighted_input(hidden, experts, top, ff, dtype):
     part = build_part("feed_forward", PartSpec("routed_experts", {
         "hidden_size": hidden, "experts": experts, "top": top, "intermediate_size": ff, "score": "sigmoid", "weight_on": "input",

@@ -43,7 +43,7 @@ def draw(i):
             rot_dim = rng.choice([4, 8, 16, 32, 64])
             kv_rank = rng.choice([16, 24, 48, 64, 128])
             layers.append(lat(rng.choice([1, 2, 3, 6, 16, 17]), rng.choice([8, 12, 16, 32, 64]), rot_dim, rng.choice([8, 12, 32, 64]),
-                              rng.choice([16, 24, 64]), kv_rank, rng.choice([0.1, 0.2]), rng.choice([100.0, 10000.0, 250000.0]), mlp(),
+                              rng.choice([16, 24, 64]), kv_rank, rng.choice([0.1, 0.2]), rng.choice([100.0, 10000.0, 200000.0]), mlp(),
                               rot_dims=rot_dim if rng.random() < 0.8 else rot_dim // 2))
     loop = None
     if rng.random() < 0.8:
